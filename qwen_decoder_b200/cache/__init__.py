@@ -1,8 +1,8 @@
-from .manager import CacheGroup, CacheLayout, CacheManager, FixedState, PagedKV, RequestCache
+from .manager import CacheGroup, CacheLayout, CacheManager, FixedState, PagedKV, PagedRows, RequestCache
 from .pages import BlockTable, CacheAccountingError, OutOfPages, PagePool, StateSlots
 from .prefix import PrefixIndex
 
 __all__ = [
-    "CacheGroup", "CacheLayout", "CacheManager", "FixedState", "PagedKV", "RequestCache", "BlockTable",
+    "CacheGroup", "CacheLayout", "CacheManager", "FixedState", "PagedKV", "PagedRows", "RequestCache", "BlockTable",
     "CacheAccountingError", "OutOfPages", "PagePool", "StateSlots", "PrefixIndex",
 ]

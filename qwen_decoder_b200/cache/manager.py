@@ -1,7 +1,7 @@
 """The cache manager: what each run of a layer caches, grouped by need, in pages.
 
 A mixer declares its need: ``PagedKV`` (keys and values per token, all of them or a
-window) or ``FixedState`` (a per-request tensor of fixed size), or nothing.  Runs
+window), ``PagedRows`` (one row per token) or ``FixedState`` (a per-request tensor of fixed size), or nothing.  Runs
 with equal paged needs form a *group*: one page id serves every layer of the group
 (as one page serves all layers in the reference, kv_cache.h:16-29), and every group
 has pages and block tables of its own, so that a windowed group can give pages back
@@ -31,6 +31,24 @@ class PagedKV:
     head_dim: int
     window: Optional[int] = None
 
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        return (2, self.num_kv_heads, page_size, self.head_dim)
+
+
+@dataclass(frozen=True)
+class PagedRows:
+    """One row of ``width`` numbers per token (a compressed form from which a mixer expands its keys
+    and values, with whatever else it caches beside it), paged like ``PagedKV``; a page of a layer is
+    ``[offset in page, width]``, contiguous."""
+    width: int
+    window: Optional[int] = None
+
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        return (page_size, self.width)
+
+
+PAGED_NEEDS = (PagedKV, PagedRows)
+
 
 @dataclass(frozen=True)
 class FixedState:
@@ -41,7 +59,7 @@ class FixedState:
 
 @dataclass
 class CacheGroup:
-    need: PagedKV
+    need: object          # PagedKV or PagedRows
     entries: List[int] = field(default_factory=list)   # schedule entries that own a layer here
 
 
@@ -66,7 +84,7 @@ class CacheLayout:
         fixed: Dict[int, int] = {}
         fixed_needs: List[FixedState] = []
         owners: Dict[int, int] = {}
-        by_need: Dict[PagedKV, int] = {}
+        by_need: Dict[object, int] = {}
         for e, (need, src) in enumerate(zip(needs, cache_of)):
             if src is not None:
                 if not (0 <= src < e) or cache_of[src] is not None:
@@ -82,7 +100,7 @@ class CacheLayout:
             owners[e] = e
             if need is None:
                 continue
-            if isinstance(need, PagedKV):
+            if isinstance(need, PAGED_NEEDS):
                 g = by_need.get(need)
                 if g is None:
                     g = len(groups)
@@ -139,9 +157,8 @@ class CacheManager:
         if self.device is not None:
             # one page more than the pool hands out: the rows that pad a batch write their keys and values there
             for g, grp in enumerate(layout.groups):
-                n = grp.need
                 self.kv[g] = torch.zeros(
-                    (len(grp.entries), num_pages + 1, 2, n.num_kv_heads, page_size, n.head_dim),
+                    (len(grp.entries), num_pages + 1) + tuple(grp.need.page_shape(page_size)),
                     dtype=dtype, device=self.device)
             # one slot more than requests: the padding rows of a padded decode batch update that one
             for i, need in enumerate(layout.fixed_needs):
@@ -163,8 +180,8 @@ class CacheManager:
     def bytes_per_page(layout: CacheLayout, page_size: int, dtype: torch.dtype) -> int:
         """Device bytes one page id costs over all groups and layers."""
         es = torch.empty((), dtype=dtype).element_size()
-        return sum(len(g.entries) * 2 * g.need.num_kv_heads * g.need.head_dim * page_size * es
-                   for g in layout.groups)
+        import math
+        return sum(len(g.entries) * math.prod(g.need.page_shape(page_size)) * es for g in layout.groups)
 
     def _pages_for(self, g: int, first_token: int, total_tokens: int) -> range:
         """Logical pages of group g that tokens [first_token, total_tokens) touch."""

@@ -78,12 +78,20 @@ def create_part(kind: str, name: str, **params):
     return cls(**params)
 
 
-def config_from_dict(d: Mapping[str, Any]):
-    """Typed configuration chosen by ``architectures[0]``."""
+def architecture_name(d: Mapping[str, Any]) -> str:
     archs = d.get("architectures")
-    if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of strings")
-    return lookup_architecture(archs[0]).config_cls.from_dict(d)
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    if archs is None and isinstance(d.get("architecture"), str):
+        return d["architecture"]
+    raise ConfigError("config.json: 'architectures' must be a non-empty list of strings "
+                      "(or 'architecture' one string)")
+
+
+def config_from_dict(d: Mapping[str, Any]):
+    """Typed configuration chosen by ``architectures[0]``, or by ``architecture`` (one string) in a
+    ``config.json`` that names its design that way."""
+    return lookup_architecture(architecture_name(d)).config_cls.from_dict(d)
 
 
 def load_config(model_dir: str):

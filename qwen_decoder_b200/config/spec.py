@@ -23,13 +23,15 @@ class LayerSpec:
 
     ``prefix`` is the weight-name prefix of the layer (``model.layers.3.``).
     ``norms`` maps the block's norm roles to part specs (for the pre-norm block:
-    ``input`` and ``post_mixer``).
+    ``input`` and ``post_mixer``).  ``feed_forward`` may be None where a block allows a layer
+    without one.  ``block_params``: further sizes and constants of the block itself.
     """
     prefix: str
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     norms: Dict[str, PartSpec]
+    block_params: Dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
@@ -57,3 +59,4 @@ class ModelSpec:
     final_norm: PartSpec
     final_norm_prefix: str
     lm_head_tensor: Optional[str]           # None: tied to the embedding
+    embedding_scale: float = 1.0            # the embedding row is multiplied by this constant

@@ -42,6 +42,9 @@ LIBRARIES: Dict[str, str] = {
     "sampling": "sampling.cu",
     "decode_attention_noalloc": "decode_attention_noalloc.cu",
     "prompt_exec": "prompt_exec.cu",
+    "latent_attention": "latent_attention.cu",
+    "mamba2": "mamba2.cu",
+    "moe": "moe.cu",
 }
 HEADERS = ["common.cuh", "entry_points.h"]
 # further files a library's source includes (hashed into its key)

@@ -13,25 +13,31 @@
 // x[t, :] = table[tokens[t], :]; the residual stream x is float32 in both paths.
 template <typename TW>
 __global__ void embedding_kernel(float* __restrict__ x, const TW* __restrict__ table,
-                                 const int* __restrict__ tokens, int D) {
+                                 const int* __restrict__ tokens, int D, float scale) {
   pdl_launch_dependents();
   pdl_wait();
   int t = blockIdx.x;
   const TW* row = table + (size_t)tokens[t] * D;
   float* out = x + (size_t)t * D;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) out[i] = to_float(row[i]);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) out[i] = to_float(row[i]) * scale;
+}
+
+// x[t, :] = table[tokens[t], :] * scale (a model may multiply its embedding by a constant; 1 is exact)
+extern "C" int qd_embedding_scaled(float* x, const void* table, int table_dtype, const int* tokens,
+                                   int T, int D, float scale, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (table_dtype == QD_F32)
+    qd_launch(embedding_kernel<float>, dim3(T), dim3(256), 0, stream, x, (const float*)table, tokens, D, scale);
+  else if (table_dtype == QD_BF16)
+    qd_launch(embedding_kernel<bf16>, dim3(T), dim3(256), 0, stream, x, (const bf16*)table, tokens, D, scale);
+  else
+    return QD_ERR_UNSUPPORTED;
+  return qd_last_error();
 }
 
 extern "C" int qd_embedding(float* x, const void* table, int table_dtype, const int* tokens,
                             int T, int D, cudaStream_t stream) {
-  if (T <= 0) return 0;
-  if (table_dtype == QD_F32)
-    qd_launch(embedding_kernel<float>, dim3(T), dim3(256), 0, stream, x, (const float*)table, tokens, D);
-  else if (table_dtype == QD_BF16)
-    qd_launch(embedding_kernel<bf16>, dim3(T), dim3(256), 0, stream, x, (const bf16*)table, tokens, D);
-  else
-    return QD_ERR_UNSUPPORTED;
-  return qd_last_error();
+  return qd_embedding_scaled(x, table, table_dtype, tokens, T, D, 1.0f, stream);
 }
 
 // ------------------------------------------------- residual add + RMSNorm
@@ -45,7 +51,7 @@ template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
                                    const float* __restrict__ w, TO* __restrict__ out,
                                    const int* __restrict__ rows, int D, float eps, int write_back,
-                                   int n_parts, size_t part_stride) {
+                                   int n_parts, size_t part_stride, const float* __restrict__ dscale) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float sm[];  // D values + 33 scratch
@@ -60,7 +66,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     if (delta) {
       float dsum = to_float(delta[s * D + i]);
       for (int p = 1; p < n_parts; p++) dsum += to_float(delta[p * part_stride + s * D + i]);
-      a += dsum;
+      a += dscale ? dsum * dscale[i] : dsum;
     }
     v[i] = a;
     if (write_back && delta) xr[i] = a;
@@ -79,16 +85,18 @@ template <typename TD, typename TO, int VPT>
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, const float* __restrict__ w,
                        TO* __restrict__ out, const int* __restrict__ rows, int D, float eps, int write_back,
-                       int n_parts, size_t part_stride) {
+                       int n_parts, size_t part_stride, const float* __restrict__ dscale) {
   pdl_launch_dependents();
   // the norm's weight does not come from the kernel before: it travels while that kernel is waited for, and is
   // no round trip of its own after the sum of squares
   const int n4 = D >> 2;
-  float4 v[VPT], wv[VPT];
+  float4 v[VPT], wv[VPT], sv[VPT];
 #pragma unroll
   for (int q = 0; q < VPT; q++) {
     const int i4 = threadIdx.x + q * blockDim.x;
     wv[q] = i4 < n4 ? reinterpret_cast<const float4*>(w)[i4] : make_float4(0.f, 0.f, 0.f, 0.f);
+    // a branch's output may be multiplied element by element (a layer scale) before it joins the sum
+    sv[q] = (dscale && i4 < n4) ? reinterpret_cast<const float4*>(dscale)[i4] : make_float4(1.f, 1.f, 1.f, 1.f);
   }
   pdl_wait();
   __shared__ float scratch[40];
@@ -116,13 +124,19 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, cons
 #pragma unroll
             for (int u = 0; u < 16; u++) { acc.x += d[u].x; acc.y += d[u].y; acc.z += d[u].z; acc.w += d[u].w; }
           }
+          if (dscale) { acc.x *= sv[q].x; acc.y *= sv[q].y; acc.z *= sv[q].z; acc.w *= sv[q].w; }
           a.x += acc.x; a.y += acc.y; a.z += acc.z; a.w += acc.w;
         } else {
           const bf16* dp = reinterpret_cast<const bf16*>(delta) + s * D + 4 * (size_t)i4;
           uint2 raw = *reinterpret_cast<const uint2*>(dp);
           __nv_bfloat162 d0 = *reinterpret_cast<__nv_bfloat162*>(&raw.x);
           __nv_bfloat162 d1 = *reinterpret_cast<__nv_bfloat162*>(&raw.y);
-          a.x += __low2float(d0); a.y += __high2float(d0); a.z += __low2float(d1); a.w += __high2float(d1);
+          if (dscale) {
+            a.x += __low2float(d0) * sv[q].x; a.y += __high2float(d0) * sv[q].y;
+            a.z += __low2float(d1) * sv[q].z; a.w += __high2float(d1) * sv[q].w;
+          } else {
+            a.x += __low2float(d0); a.y += __high2float(d0); a.z += __low2float(d1); a.w += __high2float(d1);
+          }
         }
         if (write_back) reinterpret_cast<float4*>(x + s * D)[i4] = a;
       }
@@ -154,9 +168,10 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, cons
 // The next launch of this library is ordered after all earlier work of its stream (no programmatic dependent launch).
 extern "C" void qd_elementwise_plain_next() { qd_plain_next_launch = true; }
 
-extern "C" int qd_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* w, void* out,
-                              int out_dtype, const int* rows, int n_rows, int D, float eps,
-                              int write_back, int n_parts, long long part_stride, cudaStream_t stream) {
+// ``dscale`` (float32 [D], or null): the branch output is multiplied by it element by element before the sum.
+extern "C" int qd_add_rmsnorm_scaled(float* x, const void* delta, int delta_dtype, const float* dscale, const float* w,
+                                     void* out, int out_dtype, const int* rows, int n_rows, int D, float eps,
+                                     int write_back, int n_parts, long long part_stride, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   size_t smem = (size_t)(D + 40) * sizeof(float);
   if (smem > 200 * 1024) return QD_ERR_UNSUPPORTED;
@@ -167,20 +182,21 @@ extern "C" int qd_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
                            (int)smem);                                                          \
     qd_launch(add_rmsnorm_kernel<TD, TO>, dim3(n_rows), dim3(256), smem, stream, x, (const TD*)delta, w, (TO*)out, rows, \
                                                               D, eps, write_back, n_parts,      \
-                                                              (size_t)part_stride);             \
+                                                              (size_t)part_stride, dscale);     \
   } while (0)
   bool dbf = delta && delta_dtype == QD_BF16;
   if (delta && delta_dtype != QD_BF16 && delta_dtype != QD_F32) return QD_ERR_UNSUPPORTED;
   if (n_parts < 1 || (n_parts > 1 && delta_dtype != QD_F32)) return QD_ERR_UNSUPPORTED;
   if (out_dtype != QD_F32 && out_dtype != QD_BF16) return QD_ERR_UNSUPPORTED;
-  bool aligned = !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15) && part_stride % 4 == 0;
+  bool aligned = !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out | (uintptr_t)dscale) & 15) &&
+                 part_stride % 4 == 0;
   if (D % 4 == 0 && D <= 8192 && aligned) {
     int n4 = D / 4;
     int vpt = n4 <= 1024 ? 1 : 2;
     int threads = ((n4 + vpt - 1) / vpt + 31) / 32 * 32;
 #define VLAUNCH(TD, TO, V)                                                                              \
     qd_launch(add_rmsnorm_vec_kernel<TD, TO, V>, dim3(n_rows), dim3(threads), 0, stream, x, (const TD*)delta, w, (TO*)out, rows, D, \
-                                                                      eps, write_back, n_parts, (size_t)part_stride)
+                                                                      eps, write_back, n_parts, (size_t)part_stride, dscale)
 #define VPICK(TD, TO) do { if (vpt == 1) VLAUNCH(TD, TO, 1); else VLAUNCH(TD, TO, 2); } while (0)
     if (out_dtype == QD_F32) { if (dbf) VPICK(bf16, float); else VPICK(float, float); }
     else { if (dbf) VPICK(bf16, bf16); else VPICK(float, bf16); }
@@ -199,31 +215,46 @@ extern "C" int qd_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
   return qd_last_error();
 }
 
+extern "C" int qd_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* w, void* out,
+                              int out_dtype, const int* rows, int n_rows, int D, float eps,
+                              int write_back, int n_parts, long long part_stride, cudaStream_t stream) {
+  return qd_add_rmsnorm_scaled(x, delta, delta_dtype, nullptr, w, out, out_dtype, rows, n_rows, D, eps, write_back,
+                               n_parts, part_stride, stream);
+}
+
 // x[t] += delta[t] with no norm after it (used when a residual is left pending at
 // the end of a schedule that does not finish with a norm).
 template <typename TD>
-__global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n, int n_parts) {
+__global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n, int n_parts,
+                                    const float* __restrict__ dscale, int D) {
   pdl_launch_dependents();
   pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float d = to_float(delta[i]);
   for (int p = 1; p < n_parts; p++) d += to_float(delta[p * n + i]);
-  x[i] += d;
+  x[i] += dscale ? d * dscale[i % D] : d;
+}
+
+extern "C" int qd_residual_add_scaled(float* x, const void* delta, int delta_dtype, long long n, int n_parts,
+                                      const float* dscale, int D, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (dscale && D <= 0) return QD_ERR_UNSUPPORTED;
+  if (n_parts < 1) return QD_ERR_UNSUPPORTED;
+  unsigned blocks = (unsigned)((n + 255) / 256);
+  if (delta_dtype == QD_F32)
+    qd_launch(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, (const float*)delta, (size_t)n, n_parts,
+              dscale, D);
+  else if (delta_dtype == QD_BF16 && n_parts == 1)
+    qd_launch(residual_add_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, x, (const bf16*)delta, (size_t)n, 1, dscale, D);
+  else
+    return QD_ERR_UNSUPPORTED;
+  return qd_last_error();
 }
 
 extern "C" int qd_residual_add(float* x, const void* delta, int delta_dtype, long long n, int n_parts,
                                cudaStream_t stream) {
-  if (n <= 0) return 0;
-  if (n_parts < 1) return QD_ERR_UNSUPPORTED;
-  unsigned blocks = (unsigned)((n + 255) / 256);
-  if (delta_dtype == QD_F32)
-    qd_launch(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, (const float*)delta, (size_t)n, n_parts);
-  else if (delta_dtype == QD_BF16 && n_parts == 1)
-    qd_launch(residual_add_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, x, (const bf16*)delta, (size_t)n, 1);
-  else
-    return QD_ERR_UNSUPPORTED;
-  return qd_last_error();
+  return qd_residual_add_scaled(x, delta, delta_dtype, n, n_parts, nullptr, 1, stream);
 }
 
 // -------------------------------------------- rotary + K/V write into pages

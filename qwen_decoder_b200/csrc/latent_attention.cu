@@ -1,0 +1,355 @@
+// Latent attention: keys and values of all heads are expanded from ONE cached row per token,
+//   row_j = [ c_j (kv_rank, RMS-normed latent) | kr_j (rot_dim, rotated key part shared by the heads) ],
+// with k_h,j = Wuk_h c_j and v_h,j = Wuv_h c_j.  The kernels never expand them: since
+//   q_h . (Wuk_h c_j) = (Wuk_h^T q_h) . c_j   and   sum_j p_j (Wuv_h c_j) = Wuv_h (sum_j p_j c_j),
+// a query is first carried into the latent space (``absorb``), attention runs over the cached rows
+// themselves -- every head of a token reads the same rows, so a CTA stages a tile of rows once for
+// all its heads -- and the result is carried out of the latent space afterwards (``expand``).
+//
+//   prep     RMS norms of the query latent and of c (float32), rotation of kr, write of the cache row
+//   absorb   qcat[t, h] = [ Wuk_h^T qn[t, h] | rotate(qr[t, h]) ]                    float32
+//   attend   o_lat[t, h] = softmax_j<=pos(qcat[t, h] . row_j * scale) c_j            float32, paged, split over keys
+//   combine  the splits' partial results into o_lat
+//   expand   out[t, h] = (Wuv_h o_lat[t, h]) * sigmoid(gate[t, h])
+//
+// Scores, softmax weights, norms and angles are float32 in both engine dtypes; the cache row and the
+// weights are the engine's dtype.  One template serves float32 and bfloat16.
+#include "common.cuh"
+
+#define LA_WARPS 8
+#define LA_TILE 32          // keys per staged tile
+#define LA_MAX_R 512        // latent size the attend kernel takes (16 accumulators a lane)
+#define LA_TT 8             // tokens per CTA in absorb and expand
+
+// ----------------------------------------------------------------------------- prep
+// u row t (float32, stride ldu): columns [q_off, q_off + q_rank) the raw query latent, [kv_off, kv_off + r + dr)
+// the raw key/value latent followed by the key part that is rotated.
+template <typename TC>
+__global__ void __launch_bounds__(256)
+latent_prep_kernel(const float* __restrict__ u, long long ldu, int q_off, int q_rank, int kv_off, int r, int dr,
+                   const float* __restrict__ wq_norm, const float* __restrict__ wkv_norm, float eps,
+                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_dims,
+                   const int* __restrict__ positions, const int* __restrict__ slot_map, TC* __restrict__ cq,
+                   TC* __restrict__ cache, int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[40];
+  const int t = blockIdx.x;
+  const float* row = u + (size_t)t * ldu;
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x) { float v = row[q_off + i]; sq = fmaf(v, v, sq); }
+  for (int i = threadIdx.x; i < r; i += blockDim.x) { float v = row[kv_off + i]; sk = fmaf(v, v, sk); }
+  sq = block_sum(sq, scratch);
+  sk = block_sum(sk, scratch);
+  const float iq = 1.0f / sqrtf(sq / (float)q_rank + eps);
+  const float ik = 1.0f / sqrtf(sk / (float)r + eps);
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
+    cq[(size_t)t * q_rank + i] = from_float<TC>(row[q_off + i] * iq * wq_norm[i]);
+  if (!write_cache) return;
+  TC* dst = cache + (size_t)slot_map[t] * (r + dr);
+  for (int i = threadIdx.x; i < r; i += blockDim.x) dst[i] = from_float<TC>(row[kv_off + i] * ik * wkv_norm[i]);
+  const int pos = positions[t];
+  const int half = rot_dims >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
+    float a = row[kv_off + r + 2 * i], b = row[kv_off + r + 2 * i + 1];
+    dst[r + 2 * i] = from_float<TC>(a * c - b * s);
+    dst[r + 2 * i + 1] = from_float<TC>(b * c + a * s);
+  }
+  for (int i = rot_dims + threadIdx.x; i < dr; i += blockDim.x) dst[r + i] = from_float<TC>(row[kv_off + r + i]);
+}
+
+// ----------------------------------------------------------------------------- absorb
+// q [T, H * (dn + dr)] float32; Wuk [H * dn, r]; qcat [T, H, r + dr] float32.
+template <typename TW>
+__global__ void __launch_bounds__(256)
+latent_absorb_kernel(const float* __restrict__ q, const TW* __restrict__ wuk, float* __restrict__ qcat, int T, int H,
+                     int dn, int dr, int r, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                     int rot_dims, const int* __restrict__ positions) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float qs[];                // [LA_TT][dn]
+  const int h = blockIdx.y, t0 = blockIdx.x * LA_TT;
+  const int nt = min(LA_TT, T - t0);
+  const int W = r + dr, qw = H * (dn + dr);
+  for (int i = threadIdx.x; i < LA_TT * dn; i += blockDim.x) {
+    int tt = i / dn, d = i - tt * dn;
+    qs[i] = tt < nt ? q[(size_t)(t0 + tt) * qw + (size_t)h * (dn + dr) + d] : 0.f;
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < r; j += blockDim.x) {
+    float acc[LA_TT];
+#pragma unroll
+    for (int tt = 0; tt < LA_TT; tt++) acc[tt] = 0.f;
+    const TW* wcol = wuk + (size_t)h * dn * r + j;
+    for (int d = 0; d < dn; d++) {
+      float w = to_float(wcol[(size_t)d * r]);
+#pragma unroll
+      for (int tt = 0; tt < LA_TT; tt++) acc[tt] = fmaf(qs[tt * dn + d], w, acc[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < LA_TT; tt++)
+      if (tt < nt) qcat[((size_t)(t0 + tt) * H + h) * W + j] = acc[tt];
+  }
+  const int half = rot_dims >> 1;
+  for (int i = threadIdx.x; i < nt * dr; i += blockDim.x) {
+    int tt = i / dr, e = i - tt * dr;
+    const float* qr = q + (size_t)(t0 + tt) * qw + (size_t)h * (dn + dr) + dn;
+    float v;
+    if (e < rot_dims) {
+      int pr = e >> 1, pos = positions[t0 + tt];
+      float c = cos_t[(size_t)pos * half + pr], s = sin_t[(size_t)pos * half + pr];
+      float a = qr[2 * pr], b = qr[2 * pr + 1];
+      v = (e & 1) ? b * c + a * s : a * c - b * s;
+    } else {
+      v = qr[e];
+    }
+    qcat[((size_t)(t0 + tt) * H + h) * W + r + e] = v;
+  }
+}
+
+// ----------------------------------------------------------------------------- attend
+// grid (tokens, head groups of LA_WARPS, splits).  Warp w of a CTA owns head hg * LA_WARPS + w; a tile of
+// LA_TILE cached rows is staged in shared memory as float32 once for all the CTA's heads.  Lane j scores key
+// j of the tile; for the weighted sum lane l owns latent elements l, l + 32, ...
+template <typename TC>
+__global__ void __launch_bounds__(LA_WARPS * 32)
+latent_attend_kernel(const float* __restrict__ qcat, const TC* __restrict__ cache, const int* __restrict__ block_table,
+                     int max_blocks, const int* __restrict__ token_req, const int* __restrict__ positions, int H, int r,
+                     int dr, int page_size, float scale, int window, int splits, float* __restrict__ o_lat,
+                     float* __restrict__ part_o, float* __restrict__ part_ml) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  const int W = r + dr, Wp = W + 1;
+  float* rows = sm;                              // [LA_TILE][Wp]
+  float* qsm = sm + LA_TILE * Wp;                // [LA_WARPS][W]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x, h = blockIdx.y * LA_WARPS + warp, split = blockIdx.z;
+  const bool live = h < H;
+  const int pos = positions[t];
+  const int* bt = block_table + (size_t)token_req[t] * max_blocks;
+  const int key_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  // this split's share of the key tiles
+  const int tile_lo = key_lo / LA_TILE, tile_hi = pos / LA_TILE + 1;
+  const int n_tiles = tile_hi - tile_lo;
+  const int my_lo = tile_lo + (int)((long long)n_tiles * split / splits);
+  const int my_hi = tile_lo + (int)((long long)n_tiles * (split + 1) / splits);
+  float* qw = qsm + (size_t)warp * W;
+  if (live) {
+    const float* qg = qcat + ((size_t)t * H + h) * W;
+    for (int e = lane; e < W; e += 32) qw[e] = qg[e];
+  }
+  float m = -INFINITY, l = 0.f;
+  float o[LA_MAX_R / 32];
+#pragma unroll
+  for (int i = 0; i < LA_MAX_R / 32; i++) o[i] = 0.f;
+
+  for (int tile = my_lo; tile < my_hi; tile++) {
+    const int base = tile * LA_TILE;
+    __syncthreads();                             // the tile before has been read by every warp
+    for (int j = warp; j < LA_TILE; j += LA_WARPS) {
+      int key = base + j;
+      if (key < key_lo || key > pos) continue;
+      const TC* src = cache + ((size_t)bt[key / page_size] * page_size + key % page_size) * W;
+      for (int e = lane; e < W; e += 32) rows[j * Wp + e] = to_float(src[e]);
+    }
+    __syncthreads();
+    if (!live) continue;
+    const int key = base + lane;
+    const bool valid = key >= key_lo && key <= pos;
+    float s = -INFINITY;
+    if (valid) {
+      const float* kr = rows + lane * Wp;
+      float acc = 0.f;
+      for (int e = 0; e < W; e++) acc = fmaf(qw[e], kr[e], acc);
+      s = acc * scale;
+    }
+    float m_new = fmaxf(m, warp_max(s));
+    float c = expf(m - m_new);                   // m = -inf before the first key gives 0
+    float p = valid ? expf(s - m_new) : 0.f;
+    l = l * c + warp_sum(p);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < LA_MAX_R / 32; i++) o[i] *= c;
+    const int j0 = key_lo > base ? key_lo - base : 0;
+    const int j1 = pos - base + 1 < LA_TILE ? pos - base + 1 : LA_TILE;
+    for (int j = j0; j < j1; j++) {
+      float pj = __shfl_sync(0xffffffffu, p, j);
+      const float* vr = rows + j * Wp;
+#pragma unroll
+      for (int i = 0; i < LA_MAX_R / 32; i++) {
+        int e = lane + 32 * i;
+        if (e < r) o[i] = fmaf(pj, vr[e], o[i]);
+      }
+    }
+  }
+  if (!live) return;
+  if (splits == 1) {
+    float inv = 1.0f / l;
+    float* dst = o_lat + ((size_t)t * H + h) * r;
+#pragma unroll
+    for (int i = 0; i < LA_MAX_R / 32; i++) {
+      int e = lane + 32 * i;
+      if (e < r) dst[e] = o[i] * inv;
+    }
+  } else {
+    size_t item = ((size_t)t * H + h) * splits + split;
+    float* dst = part_o + item * r;
+#pragma unroll
+    for (int i = 0; i < LA_MAX_R / 32; i++) {
+      int e = lane + 32 * i;
+      if (e < r) dst[e] = o[i];
+    }
+    if (lane == 0) { part_ml[2 * item] = m; part_ml[2 * item + 1] = l; }
+  }
+}
+
+// o_lat[t, h] = sum_s exp(m_s - M) o_s / sum_s exp(m_s - M) l_s; a split without keys has m = -inf and l = 0.
+__global__ void latent_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,
+                                      int r, float* __restrict__ o_lat) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t item = blockIdx.x;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; s++) M = fmaxf(M, part_ml[2 * (item * splits + s)]);
+  float L = 0.f;
+  for (int s = 0; s < splits; s++) {
+    float ms = part_ml[2 * (item * splits + s)];
+    if (ms > -INFINITY) L += expf(ms - M) * part_ml[2 * (item * splits + s) + 1];
+  }
+  for (int e = threadIdx.x; e < r; e += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; s++) {
+      float ms = part_ml[2 * (item * splits + s)];
+      if (ms > -INFINITY) acc = fmaf(expf(ms - M), part_o[(item * splits + s) * r + e], acc);
+    }
+    o_lat[item * r + e] = acc / L;
+  }
+}
+
+// ----------------------------------------------------------------------------- expand
+// out[t, h * dv + i] = (sum_j Wuv[h * dv + i, j] o_lat[t, h, j]) * sigmoid(gate[t, h * dv + i]); gate float32 with
+// row stride ldg (null: no gate).  A warp per output row of Wuv, LA_TT tokens a CTA.
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+latent_expand_kernel(const float* __restrict__ o_lat, const TW* __restrict__ wuv, const float* __restrict__ gate,
+                     long long ldg, TO* __restrict__ out, int T, int H, int dv, int r) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float os[];                // [LA_TT][r]
+  const int h = blockIdx.y, t0 = blockIdx.x * LA_TT;
+  const int nt = min(LA_TT, T - t0);
+  for (int i = threadIdx.x; i < LA_TT * r; i += blockDim.x) {
+    int tt = i / r, j = i - tt * r;
+    os[i] = tt < nt ? o_lat[((size_t)(t0 + tt) * H + h) * r + j] : 0.f;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int i = warp; i < dv; i += nw) {
+    const TW* wrow = wuv + ((size_t)h * dv + i) * r;
+    float acc[LA_TT];
+#pragma unroll
+    for (int tt = 0; tt < LA_TT; tt++) acc[tt] = 0.f;
+    for (int j = lane; j < r; j += 32) {
+      float w = to_float(wrow[j]);
+#pragma unroll
+      for (int tt = 0; tt < LA_TT; tt++) acc[tt] = fmaf(w, os[tt * r + j], acc[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < LA_TT; tt++) acc[tt] = warp_sum(acc[tt]);
+    if (lane == 0) {
+#pragma unroll
+      for (int tt = 0; tt < LA_TT; tt++) {
+        if (tt >= nt) continue;
+        float v = acc[tt];
+        if (gate) {
+          float g = gate[(size_t)(t0 + tt) * ldg + (size_t)h * dv + i];
+          v *= 1.0f / (1.0f + expf(-g));
+        }
+        out[(size_t)(t0 + tt) * H * dv + (size_t)h * dv + i] = from_float<TO>(v);
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- launchers
+extern "C" int qd_latent_prep(const float* u, long long ldu, int q_off, int q_rank, int kv_off, int r, int dr,
+                              const float* wq_norm, const float* wkv_norm, float eps, const float* cos_t,
+                              const float* sin_t, int rot_dims, const int* positions, const int* slot_map, void* cq,
+                              void* cache, int dtype, int write_cache, int T, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (rot_dims % 2 || rot_dims > dr || q_rank <= 0 || r <= 0) return QD_ERR_UNSUPPORTED;
+  if (dtype == QD_F32)
+    qd_launch(latent_prep_kernel<float>, dim3(T), dim3(256), 0, stream, u, ldu, q_off, q_rank, kv_off, r, dr, wq_norm,
+              wkv_norm, eps, cos_t, sin_t, rot_dims, positions, slot_map, (float*)cq, (float*)cache, write_cache);
+  else if (dtype == QD_BF16)
+    qd_launch(latent_prep_kernel<bf16>, dim3(T), dim3(256), 0, stream, u, ldu, q_off, q_rank, kv_off, r, dr, wq_norm,
+              wkv_norm, eps, cos_t, sin_t, rot_dims, positions, slot_map, (bf16*)cq, (bf16*)cache, write_cache);
+  else
+    return QD_ERR_UNSUPPORTED;
+  return qd_last_error();
+}
+
+extern "C" int qd_latent_absorb(const float* q, const void* wuk, int w_dtype, float* qcat, int T, int H, int dn, int dr,
+                                int r, const float* cos_t, const float* sin_t, int rot_dims, const int* positions,
+                                cudaStream_t stream) {
+  if (T <= 0) return 0;
+  size_t smem = (size_t)LA_TT * dn * sizeof(float);
+  if (smem > 48 * 1024 || H > 65535) return QD_ERR_UNSUPPORTED;
+  dim3 grid((T + LA_TT - 1) / LA_TT, H);
+  if (w_dtype == QD_F32)
+    qd_launch(latent_absorb_kernel<float>, grid, dim3(256), smem, stream, q, (const float*)wuk, qcat, T, H, dn, dr, r,
+              cos_t, sin_t, rot_dims, positions);
+  else if (w_dtype == QD_BF16)
+    qd_launch(latent_absorb_kernel<bf16>, grid, dim3(256), smem, stream, q, (const bf16*)wuk, qcat, T, H, dn, dr, r,
+              cos_t, sin_t, rot_dims, positions);
+  else
+    return QD_ERR_UNSUPPORTED;
+  return qd_last_error();
+}
+
+extern "C" int qd_latent_attend(const float* qcat, const void* cache, int dtype, const int* block_table, int max_blocks,
+                                const int* token_req, const int* positions, int T, int H, int r, int dr, int page_size,
+                                float scale, int window, int splits, float* o_lat, float* part_o, float* part_ml,
+                                cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (r > LA_MAX_R || r <= 0 || splits < 1 || splits > 65535 || H > 65535 * LA_WARPS || page_size <= 0) return QD_ERR_UNSUPPORTED;
+  if (splits > 1 && (!part_o || !part_ml)) return QD_ERR_UNSUPPORTED;
+  const int W = r + dr;
+  size_t smem = ((size_t)LA_TILE * (W + 1) + (size_t)LA_WARPS * W) * sizeof(float);
+  if (smem > 200 * 1024) return QD_ERR_UNSUPPORTED;
+  dim3 grid(T, (H + LA_WARPS - 1) / LA_WARPS, splits);
+#define LA_GO(TC)                                                                                                  \
+  do {                                                                                                             \
+    if (smem > 48 * 1024)                                                                                          \
+      cudaFuncSetAttribute(latent_attend_kernel<TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+    qd_launch(latent_attend_kernel<TC>, grid, dim3(LA_WARPS * 32), smem, stream, qcat, (const TC*)cache, block_table, \
+              max_blocks, token_req, positions, H, r, dr, page_size, scale, window, splits, o_lat, part_o, part_ml); \
+  } while (0)
+  if (dtype == QD_F32) LA_GO(float);
+  else if (dtype == QD_BF16) LA_GO(bf16);
+  else return QD_ERR_UNSUPPORTED;
+#undef LA_GO
+  if (splits > 1)
+    qd_launch(latent_combine_kernel, dim3((unsigned)((size_t)T * H)), dim3(128), 0, stream, (const float*)part_o,
+              (const float*)part_ml, splits, r, o_lat);
+  return qd_last_error();
+}
+
+extern "C" int qd_latent_expand(const float* o_lat, const void* wuv, int w_dtype, const float* gate, long long ldg,
+                                void* out, int out_dtype, int T, int H, int dv, int r, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  size_t smem = (size_t)LA_TT * r * sizeof(float);
+  if (smem > 48 * 1024 || H > 65535) return QD_ERR_UNSUPPORTED;
+  dim3 grid((T + LA_TT - 1) / LA_TT, H);
+  if (w_dtype == QD_F32 && out_dtype == QD_F32)
+    qd_launch(latent_expand_kernel<float, float>, grid, dim3(256), smem, stream, o_lat, (const float*)wuv, gate, ldg,
+              (float*)out, T, H, dv, r);
+  else if (w_dtype == QD_BF16 && out_dtype == QD_BF16)
+    qd_launch(latent_expand_kernel<bf16, bf16>, grid, dim3(256), smem, stream, o_lat, (const bf16*)wuv, gate, ldg,
+              (bf16*)out, T, H, dv, r);
+  else
+    return QD_ERR_UNSUPPORTED;
+  return qd_last_error();
+}

@@ -21,7 +21,7 @@ from .batch import StepEntry
 from .runner import ModelRunner
 
 DEFAULT_PAGE_SIZE = 16
-DEFAULT_MAX_LIVE = 8
+DEFAULT_MAX_LIVE = 4
 
 
 def pool_pages(max_tokens: int, page_size: int = DEFAULT_PAGE_SIZE, max_live: int = DEFAULT_MAX_LIVE) -> int:
@@ -83,8 +83,10 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     if args.page_size < 1 or args.max_live < 1:
         ap.error("--page-size and --max-live must be at least 1")
-    runner = ModelRunner.from_folder(args.model, dtype=args.dtype, device=args.device,
-                                     num_pages=pool_pages(args.max_tokens, args.page_size, args.max_live),
-                                     page_size=args.page_size, max_requests=args.max_live)
+    pages = pool_pages(args.max_tokens, args.page_size, args.max_live)
+    # no request can be longer than the pool: position tables need not reach further
+    runner = ModelRunner.from_folder(args.model, dtype=args.dtype, device=args.device, num_pages=pages,
+                                     page_size=args.page_size, max_requests=args.max_live,
+                                     max_positions=pages * args.page_size)
     replay(runner, sys.stdin, args.out, sys.stdout)
     return 0

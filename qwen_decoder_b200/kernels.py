@@ -91,19 +91,21 @@ _I, _LL, _F = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 
 
 # ------------------------------------------------------------------ elementwise
-def embedding(x_out: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor) -> None:
-    """x_out[t, :] = table[tokens[t], :]; x_out float32 [T, D], tokens int32 [T]."""
+def embedding(x_out: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, scale: float = 1.0) -> None:
+    """x_out[t, :] = table[tokens[t], :] * scale; x_out float32 [T, D], tokens int32 [T]."""
     T, D = x_out.shape
     assert x_out.dtype == torch.float32 and tokens.dtype == torch.int32 and table.shape[1] == D
     _contig(x_out, "x_out"); _contig(table, "table")
-    _check(library("elementwise").qd_embedding(_ptr(x_out), _ptr(table), _I(dtype_code(table.dtype)),
-                                               _ptr(tokens), _I(T), _I(D), _stream()), "embedding")
+    _check(library("elementwise").qd_embedding_scaled(_ptr(x_out), _ptr(table), _I(dtype_code(table.dtype)),
+                                                      _ptr(tokens), _I(T), _I(D), _F(scale), _stream()), "embedding")
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
-                eps: float, rows: Optional[torch.Tensor] = None, write_back: bool = True) -> None:
+                eps: float, rows: Optional[torch.Tensor] = None, write_back: bool = True,
+                delta_scale: Optional[torch.Tensor] = None) -> None:
     """out[r] = rmsnorm(x[s] + delta[s]) * weight with s = rows[r] (or r); x float32 [T, D] is
-    updated to x + delta when ``write_back``."""
+    updated to x + delta when ``write_back``.  ``delta_scale`` (float32 [D]): delta is multiplied by it,
+    element by element along D, before it is added."""
     D = x.shape[1]
     n_rows = out.shape[0]
     assert x.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == D
@@ -119,17 +121,30 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
         else:
             assert delta.shape == x.shape
         _contig(delta, "delta")
+    if delta_scale is not None and delta is not None:
+        assert delta_scale.dtype == torch.float32 and delta_scale.numel() == D and delta_scale.is_contiguous()
+        _check(library("elementwise").qd_add_rmsnorm_scaled(
+            _ptr(x), _ptr(delta), _I(dtype_code(delta.dtype)), _ptr(delta_scale), _ptr(weight),
+            _ptr(out), _I(dtype_code(out.dtype)), _ptr(rows), _I(n_rows), _I(D), _F(eps),
+            _I(1 if write_back else 0), _I(n_parts), _LL(x.numel()), _stream()), "add_rmsnorm")
+        return
     _check(library("elementwise").qd_add_rmsnorm(
         _ptr(x), _ptr(delta), _I(dtype_code(delta.dtype) if delta is not None else -1), _ptr(weight),
         _ptr(out), _I(dtype_code(out.dtype)), _ptr(rows), _I(n_rows), _I(D), _F(eps),
         _I(1 if write_back else 0), _I(n_parts), _LL(x.numel()), _stream()), "add_rmsnorm")
 
 
-def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
-    """x += delta (delta [T, D], or float32 partial sums [n_parts, T, D])."""
+def residual_add(x: torch.Tensor, delta: torch.Tensor, delta_scale: Optional[torch.Tensor] = None) -> None:
+    """x += delta (delta [T, D], or float32 partial sums [n_parts, T, D]), times ``delta_scale`` [D] if given."""
     n_parts = delta.shape[0] if delta.dim() == 3 else 1
     assert x.dtype == torch.float32 and tuple(x.shape) == tuple(delta.shape[-2:])
     _contig(x, "x"); _contig(delta, "delta")
+    if delta_scale is not None:
+        assert delta_scale.dtype == torch.float32 and delta_scale.numel() == x.shape[1]
+        _check(library("elementwise").qd_residual_add_scaled(
+            _ptr(x), _ptr(delta), _I(dtype_code(delta.dtype)), _LL(x.numel()), _I(n_parts), _ptr(delta_scale),
+            _I(x.shape[1]), _stream()), "residual_add")
+        return
     _check(library("elementwise").qd_residual_add(_ptr(x), _ptr(delta), _I(dtype_code(delta.dtype)),
                                                   _LL(x.numel()), _I(n_parts), _stream()), "residual_add")
 
@@ -680,6 +695,181 @@ def wait_probe(name: str, poll_limit: int = 2048) -> None:
     function, on an mbarrier that nobody arrives at.  The wait runs out, the kernel ends, and the next
     ``check_status`` raises.  For tests of that chain; it harms nothing else."""
     _check(getattr(library(name), _STATUS[name][1])(ctypes.c_uint(poll_limit), _stream()), f"{name} wait probe")
+
+
+# ------------------------------------------------------------------ latent attention
+LATENT_MAX_RANK = 512
+
+
+def latent_prep(u: torch.Tensor, q_off: int, q_rank: int, kv_off: int, r: int, dr: int, wq_norm: torch.Tensor,
+                wkv_norm: torch.Tensor, eps: float, cos: torch.Tensor, sin: torch.Tensor, rot_dims: int,
+                positions: torch.Tensor, slot_map: torch.Tensor, cq: torch.Tensor, cache: torch.Tensor,
+                write_cache: bool) -> None:
+    """From the float32 projections u [T, *]: cq [T, q_rank] = RMS norm of the query latent times its weight, and
+    the cache row [normed latent (r) | rotated key part (dr)] written to each token's slot of ``cache``
+    [pages, page_size, r + dr].  Norms and rotation in float32; ``rot_dims`` leading elements of the key part turn,
+    pairs (2i, 2i + 1)."""
+    T = u.shape[0]
+    assert u.dtype == torch.float32 and u.stride(1) == 1 and cq.shape == (T, q_rank) and cq.dtype == cache.dtype
+    assert cache.shape[-1] == r + dr and wq_norm.dtype == wkv_norm.dtype == torch.float32
+    assert cos.dtype == torch.float32 and cos.shape[1] == rot_dims // 2 and positions.dtype == torch.int32
+    _contig(cq, "cq"); _contig(cache, "cache")
+    _check(library("latent_attention").qd_latent_prep(
+        _ptr(u), _LL(u.stride(0)), _I(q_off), _I(q_rank), _I(kv_off), _I(r), _I(dr), _ptr(wq_norm), _ptr(wkv_norm),
+        _F(eps), _ptr(cos), _ptr(sin), _I(rot_dims), _ptr(positions), _ptr(slot_map), _ptr(cq), _ptr(cache),
+        _I(dtype_code(cache.dtype)), _I(1 if write_cache else 0), _I(T), _stream()), "latent_prep")
+
+
+def latent_absorb(q: torch.Tensor, wuk: torch.Tensor, qcat: torch.Tensor, H: int, dn: int, dr: int, r: int,
+                  cos: torch.Tensor, sin: torch.Tensor, rot_dims: int, positions: torch.Tensor) -> None:
+    """qcat[t, h] = [Wuk_h^T q_unrotated[t, h] (r) | rotate(q_rotated[t, h]) (dr)], float32; q float32
+    [T, H * (dn + dr)], wuk [H * dn, r]."""
+    T = q.shape[0]
+    assert q.dtype == torch.float32 and q.shape == (T, H * (dn + dr)) and wuk.shape == (H * dn, r)
+    assert qcat.dtype == torch.float32 and qcat.shape == (T, H, r + dr)
+    _contig(q, "q"); _contig(wuk, "wuk"); _contig(qcat, "qcat")
+    _check(library("latent_attention").qd_latent_absorb(
+        _ptr(q), _ptr(wuk), _I(dtype_code(wuk.dtype)), _ptr(qcat), _I(T), _I(H), _I(dn), _I(dr), _I(r), _ptr(cos),
+        _ptr(sin), _I(rot_dims), _ptr(positions), _stream()), "latent_absorb")
+
+
+def latent_attend(qcat: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, token_req: torch.Tensor,
+                  positions: torch.Tensor, r: int, dr: int, page_size: int, scale: float, window: int, splits: int,
+                  o_lat: torch.Tensor) -> None:
+    """o_lat[t, h] = sum_j softmax_j(qcat[t, h] . row_j * scale) row_j[:r] over the cached rows j <= position of the
+    token's request (``cache`` [pages, page_size, r + dr] through ``block_table``); float32 scores and weights;
+    ``splits`` CTAs share a token's keys."""
+    T, H, W = qcat.shape
+    assert W == r + dr and o_lat.shape == (T, H, r) and o_lat.dtype == torch.float32 and qcat.dtype == torch.float32
+    assert tuple(cache.shape[1:]) == (page_size, W) and block_table.dtype == torch.int32 and block_table.dim() == 2
+    _contig(qcat, "qcat"); _contig(cache, "cache"); _contig(block_table, "block_table"); _contig(o_lat, "o_lat")
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty((T * H * splits, r), dtype=torch.float32, device=qcat.device)
+        part_ml = torch.empty((T * H * splits, 2), dtype=torch.float32, device=qcat.device)
+    _check(library("latent_attention").qd_latent_attend(
+        _ptr(qcat), _ptr(cache), _I(dtype_code(cache.dtype)), _ptr(block_table), _I(block_table.shape[1]),
+        _ptr(token_req), _ptr(positions), _I(T), _I(H), _I(r), _I(dr), _I(page_size), _F(scale), _I(window),
+        _I(splits), _ptr(o_lat), _ptr(part_o), _ptr(part_ml), _stream()), "latent_attend")
+    if splits > 1:
+        _launch_count[0] += 1
+
+
+def latent_expand(o_lat: torch.Tensor, wuv: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor,
+                  dv: int) -> None:
+    """out[t, h * dv + i] = (Wuv_h o_lat[t, h])[i] * sigmoid(gate[t, h * dv + i]); gate float32 (a column slice of a
+    wider buffer is fine) or None."""
+    T, H, r = o_lat.shape
+    assert wuv.shape == (H * dv, r) and out.shape == (T, H * dv) and out.dtype == wuv.dtype
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape == (T, H * dv) and gate.stride(1) == 1)
+    _contig(o_lat, "o_lat"); _contig(wuv, "wuv"); _contig(out, "out")
+    _check(library("latent_attention").qd_latent_expand(
+        _ptr(o_lat), _ptr(wuv), _I(dtype_code(wuv.dtype)), _ptr(gate), _LL(gate.stride(0) if gate is not None else 0),
+        _ptr(out), _I(dtype_code(out.dtype)), _I(T), _I(H), _I(dv), _I(r), _stream()), "latent_expand")
+
+
+# ------------------------------------------------------------------ state-space mixer
+def mamba_conv(u: torch.Tensor, x_off: int, C: int, taps: int, w: torch.Tensor, bias: torch.Tensor,
+               state: torch.Tensor, conv_off: int, token_req: torch.Tensor, cu_tokens: torch.Tensor,
+               slots: torch.Tensor, xbc: torch.Tensor, n_requests: int, update_state: bool) -> None:
+    """xbc[t, c] = silu(bias[c] + sum_k w[c, k] * input[t - (taps - 1) + k, c]) over columns x_off.. of u (float32);
+    inputs before a request's portion come from its state row (``state`` [slots, n], the last taps - 1 inputs at
+    ``conv_off``, oldest first), which is then moved on by the portion when ``update_state``."""
+    T = u.shape[0]
+    assert u.dtype == torch.float32 and u.stride(1) == 1 and xbc.shape == (T, C) and xbc.dtype == torch.float32
+    assert w.shape == (C, taps) and w.dtype == bias.dtype == torch.float32 and state.dtype == torch.float32
+    _contig(w, "w"); _contig(xbc, "xbc"); _contig(state, "state")
+    _check(library("mamba2").qd_mamba_conv(
+        _ptr(u), _LL(u.stride(0)), _I(x_off), _I(C), _I(taps), _ptr(w), _ptr(bias), _ptr(state), _LL(state.stride(0)),
+        _LL(conv_off), _ptr(token_req), _ptr(cu_tokens), _ptr(slots), _ptr(xbc), _I(T), _I(n_requests),
+        _I(1 if update_state else 0), _stream()), "mamba_conv")
+    if update_state and taps > 1:
+        _launch_count[0] += 1
+
+
+def mamba_scan(xbc: torch.Tensor, u: torch.Tensor, dt_off: int, dt_bias: torch.Tensor, A_log: torch.Tensor,
+               D: torch.Tensor, state: torch.Tensor, cu_tokens: torch.Tensor, slots: torch.Tensor, y: torch.Tensor,
+               n_requests: int, nh: int, P: int, N: int, G: int, write_state: bool = True) -> None:
+    """The recurrence, request by request and head by head over the portion's tokens, float32:
+    dt = softplus(u[t, dt_off + h] + dt_bias[h]); S <- exp(-exp(A_log[h]) dt) S + dt B x^T; y = S^T C + D[h] x, with
+    xbc rows [x (nh * P) | B (G * N) | C (G * N)] and S [nh, P, N] at the start of the request's state row."""
+    T = xbc.shape[0]
+    assert xbc.dtype == u.dtype == y.dtype == state.dtype == torch.float32 and y.shape == (T, nh * P)
+    assert xbc.shape[1] == nh * P + 2 * G * N and state.shape[1] >= nh * P * N
+    _contig(xbc, "xbc"); _contig(y, "y"); _contig(state, "state")
+    _check(library("mamba2").qd_mamba_scan(
+        _ptr(xbc), _I(xbc.shape[1]), _ptr(u), _LL(u.stride(0)), _I(dt_off), _ptr(dt_bias), _ptr(A_log), _ptr(D),
+        _ptr(state), _LL(state.stride(0)), _ptr(cu_tokens), _ptr(slots), _ptr(y), _I(n_requests), _I(nh), _I(P),
+        _I(N), _I(G), _I(1 if write_state else 0), _stream()), "mamba_scan")
+
+
+def mamba_gate_norm(y: torch.Tensor, u: torch.Tensor, z_off: int, w: torch.Tensor, out: torch.Tensor, groups: int,
+                    eps: float) -> None:
+    """out = v / sqrt(mean(v^2) + eps) * w over each of ``groups`` equal parts of v = y * silu(u[:, z_off:...])."""
+    T, inner = y.shape
+    assert y.dtype == u.dtype == w.dtype == torch.float32 and out.shape == (T, inner) and w.numel() == inner
+    _contig(y, "y"); _contig(out, "out")
+    _check(library("mamba2").qd_mamba_gate_norm(
+        _ptr(y), _ptr(u), _LL(u.stride(0)), _I(z_off), _ptr(w), _ptr(out), _I(dtype_code(out.dtype)), _I(T),
+        _I(inner), _I(groups), _F(eps), _stream()), "mamba_gate_norm")
+
+
+# ------------------------------------------------------------------ routed experts
+MOE_MAX_TOP = 32
+
+
+def moe_route(h: torch.Tensor, wr: torch.Tensor, br: torch.Tensor, wsg: Optional[torch.Tensor], top: int,
+              idx: torch.Tensor, wt: torch.Tensor, sgate: Optional[torch.Tensor]) -> None:
+    """idx, wt [T, top]: the ``top`` experts with the largest float32 logits wr h + br and the softmax over those
+    logits; sgate[t] = sigmoid(wsg . h[t]) when a shared expert's gate vector is given."""
+    T, D = h.shape
+    E = wr.shape[0]
+    assert wr.shape == (E, D) and wr.dtype == h.dtype and br.dtype == torch.float32 and br.numel() == E
+    assert idx.dtype == torch.int32 and wt.dtype == torch.float32 and idx.shape == wt.shape == (T, top)
+    _contig(h, "h"); _contig(wr, "wr")
+    _check(library("moe").qd_moe_route(_ptr(h), _ptr(wr), _ptr(br), _ptr(wsg), _I(dtype_code(h.dtype)), _I(T), _I(D),
+                                       _I(E), _I(top), _ptr(idx), _ptr(wt), _ptr(sgate), _stream()), "moe_route")
+
+
+def moe_sort(idx: torch.Tensor, E: int, tile_rows: int, max_tiles: int, place: torch.Tensor, pair_at: torch.Tensor,
+             meta: torch.Tensor) -> None:
+    """Order the (token, choice) pairs by expert on the device: place[pair], pair_at[place], and ``meta`` =
+    [offsets (E + 1) | number of tiles | (expert, first row, rows) per tile]."""
+    n = idx.numel()
+    assert place.numel() == n and pair_at.numel() == n and meta.numel() >= E + 2 + 3 * max_tiles
+    _check(library("moe").qd_moe_sort(_ptr(idx), _I(n), _I(E), _I(tile_rows), _I(max_tiles), _ptr(place),
+                                      _ptr(pair_at), _ptr(meta), _stream()), "moe_sort")
+
+
+def moe_gemm(a: torch.Tensor, pair_at: torch.Tensor, top: int, by_token: bool, w1: torch.Tensor,
+             w2: Optional[torch.Tensor], out: torch.Tensor, meta: torch.Tensor, tile_rows: int, max_tiles: int) -> None:
+    """Grouped product over the sorted pairs: out[place] = a_row W1[e]^T (or, with w2, silu(a W1[e]^T) * (a W2[e]^T));
+    a_row = a[token of the pair] when ``by_token`` else a[place]; w [E, N, K]."""
+    E, N, K = w1.shape
+    assert a.shape[1] == K and a.stride(1) == 1 and out.shape[1] == N and (w2 is None or w2.shape == w1.shape)
+    _contig(w1, "w1"); _contig(out, "out")
+    _check(library("moe").qd_moe_gemm(
+        _ptr(a), _LL(a.stride(0)), _I(dtype_code(a.dtype)), _ptr(pair_at), _I(top), _I(1 if by_token else 0), _ptr(w1),
+        _ptr(w2), _I(dtype_code(w1.dtype)), _ptr(out), _I(dtype_code(out.dtype)), _I(N), _I(K), _ptr(meta), _I(E),
+        _I(tile_rows), _I(max_tiles), _I(1 if w2 is not None else 0), _stream()), "moe_gemm")
+
+
+def moe_combine(y: torch.Tensor, place: torch.Tensor, wt: torch.Tensor, shared: Optional[torch.Tensor],
+                sgate: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[t] = sum_k wt[t, k] y[place[t, k]] + sgate[t] * shared[t] (shared [T, D], or float32 partial sums
+    [n, T, D]); out float32."""
+    T, D = out.shape
+    top = wt.shape[1]
+    assert y.dtype == torch.float32 and out.dtype == torch.float32 and y.shape[1] == D
+    n_parts, stride = 1, 0
+    if shared is not None:
+        if shared.dim() == 3:
+            n_parts, stride = shared.shape[0], T * D
+            assert shared.dtype == torch.float32
+        _contig(shared, "shared")
+    _check(library("moe").qd_moe_combine(
+        _ptr(y), _ptr(place), _ptr(wt), _I(top), _ptr(shared), _I(dtype_code(shared.dtype) if shared is not None else 0),
+        _I(n_parts), _LL(stride), _ptr(sgate), _ptr(out), _I(T), _I(D), _stream()), "moe_combine")
 
 
 # ------------------------------------------------------------------ the layers of a prompt step from native code

@@ -53,16 +53,19 @@ class ResidualStream:
     def __init__(self, x: torch.Tensor):
         self.x = x
         self.delta: Optional[torch.Tensor] = None
+        self.delta_scale: Optional[torch.Tensor] = None     # float32 [D]: a layer scale on the pending branch
 
-    def push(self, delta: torch.Tensor) -> None:
-        """Hand over a branch output; a delta still pending is added first."""
+    def push(self, delta: torch.Tensor, scale: Optional[torch.Tensor] = None) -> None:
+        """Hand over a branch output (times ``scale`` along D, if given); a delta still pending is added first."""
         self.flush()
         self.delta = delta
+        self.delta_scale = scale
 
     def flush(self) -> None:
         if self.delta is not None:
-            kernels.residual_add(self.x, self.delta)
+            kernels.residual_add(self.x, self.delta, self.delta_scale)
             self.delta = None
+            self.delta_scale = None
 
 
 @dataclass

@@ -60,3 +60,48 @@ class PreNormBlock(Block):
         stream.push(self.mixer.forward(h, ctx, cache))
         h = self.post_mixer_norm.forward(stream, self.dtype)
         stream.push(self.feed_forward.forward(h, ctx))
+
+
+@register_part("block", "pre_norm_scaled")
+class ScaledPreNormBlock(PreNormBlock):
+    """The pre-norm block with a layer scale: each branch's output is multiplied, element by element along
+    the hidden size, by a learned vector before it joins the residual sum,
+    x += s1 * mixer(norm(x)); x += s2 * feed_forward(norm(x)).  The multiplication happens in float32 inside
+    the kernel that adds the branch (the next norm's).  A layer may have no feed-forward: the block then ends
+    after the mixer and needs no second norm."""
+
+    def __init__(self, mixer: Mixer, feed_forward, norms: Dict[str, Norm], size: int, prefix: str = "",
+                 scale_names=("ls1", "ls2")):
+        if feed_forward is None:
+            norms = dict(norms)
+            norms.setdefault("post_mixer", None)
+        super().__init__(mixer, feed_forward, norms)
+        self.size = size
+        self.prefix = prefix
+        self.scale_names = tuple(scale_names)
+        self.mixer_scale = None
+        self.ff_scale = None
+
+    def parts(self):
+        return [p for p in super().parts() if p is not None]
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        specs = super().tensor_specs()
+        specs.append(TensorSpec(f"{self.prefix}{self.scale_names[0]}", (self.size,), init="around_one"))
+        if self.feed_forward is not None:
+            specs.append(TensorSpec(f"{self.prefix}{self.scale_names[1]}", (self.size,), init="around_one"))
+        return specs
+
+    def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
+        super().bind(source, dtype, device)
+        get = lambda n: source.get(f"{self.prefix}{n}").to(device=device, dtype=torch.float32).contiguous()
+        self.mixer_scale = get(self.scale_names[0])
+        if self.feed_forward is not None:
+            self.ff_scale = get(self.scale_names[1])
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        h = self.input_norm.forward(stream, self.dtype)
+        stream.push(self.mixer.forward(h, ctx, cache), self.mixer_scale)
+        if self.feed_forward is not None:
+            h = self.post_mixer_norm.forward(stream, self.dtype)
+            stream.push(self.feed_forward.forward(h, ctx), self.ff_scale)

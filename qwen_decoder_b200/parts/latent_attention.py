@@ -1,0 +1,100 @@
+"""Latent attention: queries and keys/values go through low-rank latents, and only one row per token is
+cached, [normed key/value latent | rotated key part shared by all heads].
+
+With h the mixer's input [T, D], H heads of ``nope_dim`` unrotated + ``rope_dim`` rotated query/key elements and
+``v_dim`` value elements, latent sizes ``q_rank`` and ``kv_rank``:
+
+    cq = rms(Wdq h) * w_dq            q = Wuq cq, per head [nope | rope]
+    [c_raw | kr] = Wdkv h             c = rms(c_raw) * w_dkv;  kr and q's rope part rotated by position
+    k_h = Wuk_h c,  v_h = Wuv_h c     score = (q_nope . k_h + q_rope . kr) * scale, causal softmax
+    out = Wo ((heads' results) * sigmoid(Wg h))
+
+Keys and values are never expanded: the query is carried into the latent space (Wuk_h^T q_nope), attention runs
+over the cached rows, and Wuv_h is applied to the weighted sum of latents (``csrc/latent_attention.cu``).  Wdq,
+Wdkv and Wg are one stacked product of h.  Norms, angles, scores and softmax weights are float32 in both engine
+dtypes.  The plain norms here multiply by the stored weight (no offset); their eps is the layer's.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from .. import kernels
+from ..cache import PagedRows
+from ..config.registry import register_part
+from ..weights.loader import TensorSource, TensorSpec
+from .base import Mixer, PagedCacheView
+from .linear import Linear
+
+
+def attend_splits(ctas_without_split: int, max_keys: int) -> int:
+    """CTAs that share one token's keys: enough to give every multiprocessor one, none with fewer than four
+    tiles of 32 keys."""
+    by_fill = max(1, kernels.sm_count() // max(1, ctas_without_split))
+    by_work = max(1, (max_keys + 127) // 128)
+    return max(1, min(by_fill, by_work, 64))
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, nope_dim: int, rope_dim: int, v_dim: int, q_rank: int,
+                 kv_rank: int, scale: float, eps: float, position=None, window: Optional[int] = None,
+                 prefix: str = "self_attn.", weight_suffix: str = ".weight"):
+        if kv_rank > kernels.LATENT_MAX_RANK:
+            raise ValueError(f"latent attention: kv_rank {kv_rank} exceeds {kernels.LATENT_MAX_RANK}")
+        self.hidden_size, self.num_heads = hidden_size, num_heads
+        self.nope_dim, self.rope_dim, self.v_dim = nope_dim, rope_dim, v_dim
+        self.q_rank, self.kv_rank = q_rank, kv_rank
+        self.scale, self.eps, self.window = float(scale), float(eps), window
+        self.position = position            # a Rotary over the rope part (its rotary_dim leading elements turn) or None
+        self.prefix, self.sfx = prefix, weight_suffix
+        H = num_heads
+        self.down = Linear(hidden_size, [(f"{prefix}dq", q_rank), (f"{prefix}dkv", kv_rank + rope_dim),
+                                         (f"{prefix}g", H * v_dim)], bias=False, weight_suffix=weight_suffix)
+        self.up_q = Linear(q_rank, [(f"{prefix}uq", H * (nope_dim + rope_dim))], bias=False,
+                           weight_suffix=weight_suffix)
+        self.out = Linear(H * v_dim, [(f"{prefix}o", hidden_size)], bias=False, weight_suffix=weight_suffix)
+
+    def cache_need(self):
+        return PagedRows(self.kv_rank + self.rope_dim, self.window)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, s, H = self.prefix, self.sfx, self.num_heads
+        return self.down.tensor_specs() + self.up_q.tensor_specs() + self.out.tensor_specs() + [
+            TensorSpec(f"{p}dq.norm", (self.q_rank,), init="around_one"),
+            TensorSpec(f"{p}dkv.norm", (self.kv_rank,), init="around_one"),
+            TensorSpec(f"{p}uk{s}", (H * self.nope_dim, self.kv_rank)),
+            TensorSpec(f"{p}uv{s}", (H * self.v_dim, self.kv_rank))]
+
+    def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
+        for lin in (self.down, self.up_q, self.out):
+            lin.bind(source, dtype, device)
+        p, s = self.prefix, self.sfx
+        f32 = lambda n: source.get(n).to(device=device, dtype=torch.float32).contiguous()
+        self.w_dq_norm, self.w_dkv_norm = f32(f"{p}dq.norm"), f32(f"{p}dkv.norm")
+        self.w_uk = source.get(f"{p}uk{s}").to(device=device, dtype=dtype).contiguous()
+        self.w_uv = source.get(f"{p}uv{s}").to(device=device, dtype=dtype).contiguous()
+        self._no_table = torch.zeros((1, 0), dtype=torch.float32, device=device)
+
+    def forward(self, x: torch.Tensor, ctx, cache: PagedCacheView) -> torch.Tensor:
+        T, H = x.shape[0], self.num_heads
+        dn, dr, dv, r, qr = self.nope_dim, self.rope_dim, self.v_dim, self.kv_rank, self.q_rank
+        pos = self.position
+        rot = (pos.cos, pos.sin, pos.rotary_dim) if pos is not None else (self._no_table, self._no_table, 0)
+        u = self.down.forward(x, out_dtype=torch.float32)                   # [T, qr | r + dr | H * dv]
+        cq = torch.empty((T, qr), dtype=x.dtype, device=x.device)
+        kernels.latent_prep(u, 0, qr, qr, r, dr, self.w_dq_norm, self.w_dkv_norm, self.eps, *rot, ctx.positions,
+                            cache.group.slot_map, cq, cache.kv, cache.write)
+        q = self.up_q.forward(cq, out_dtype=torch.float32)
+        qcat = torch.empty((T, H, r + dr), dtype=torch.float32, device=x.device)
+        kernels.latent_absorb(q, self.w_uk, qcat, H, dn, dr, r, *rot, ctx.positions)
+        o_lat = torch.empty((T, H, r), dtype=torch.float32, device=x.device)
+        window = self.window or 0
+        groups = -(-H // 8)
+        splits = attend_splits(T * groups, min(ctx.max_context, window or ctx.max_context))
+        kernels.latent_attend(qcat, cache.kv, cache.group.block_table, ctx.token_request, ctx.positions, r, dr,
+                              cache.group.page_size, self.scale, window, splits, o_lat)
+        attn = torch.empty((T, H * dv), dtype=x.dtype, device=x.device)
+        kernels.latent_expand(o_lat, self.w_uv, u[:, qr + r + dr:], attn, dv)
+        return self.out.forward_partial(attn)

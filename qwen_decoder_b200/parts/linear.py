@@ -20,10 +20,13 @@ from . import matmul_backend
 
 
 class Linear:
-    def __init__(self, in_features: int, pieces: Sequence[Tuple[str, int]], bias: bool):
+    def __init__(self, in_features: int, pieces: Sequence[Tuple[str, int]], bias: bool,
+                 weight_suffix: str = ".weight", bias_suffix: str = ".bias"):
         """``pieces``: (weight-name stem, out_features) stacked in order; tensor names are
-        ``<stem>.weight`` and, with ``bias``, ``<stem>.bias``."""
+        ``<stem><weight_suffix>`` and, with ``bias``, ``<stem><bias_suffix>`` (``.weight`` and ``.bias``
+        unless a model names its tensors otherwise)."""
         self.in_features = in_features
+        self.weight_suffix, self.bias_suffix = weight_suffix, bias_suffix
         self.pieces = list(pieces)
         self.out_features = sum(n for _, n in pieces)
         self.has_bias = bias
@@ -33,16 +36,16 @@ class Linear:
     def tensor_specs(self) -> List[TensorSpec]:
         specs = []
         for stem, n in self.pieces:
-            specs.append(TensorSpec(f"{stem}.weight", (n, self.in_features)))
+            specs.append(TensorSpec(f"{stem}{self.weight_suffix}", (n, self.in_features)))
             if self.has_bias:
-                specs.append(TensorSpec(f"{stem}.bias", (n,)))
+                specs.append(TensorSpec(f"{stem}{self.bias_suffix}", (n,)))
         return specs
 
     def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
-        ws = [source.get(f"{stem}.weight").to(device=device, dtype=dtype) for stem, _ in self.pieces]
+        ws = [source.get(f"{stem}{self.weight_suffix}").to(device=device, dtype=dtype) for stem, _ in self.pieces]
         self.weight = (torch.cat(ws, dim=0) if len(ws) > 1 else ws[0]).contiguous()
         if self.has_bias:
-            bs = [source.get(f"{stem}.bias").to(device=device, dtype=torch.float32) for stem, _ in self.pieces]
+            bs = [source.get(f"{stem}{self.bias_suffix}").to(device=device, dtype=torch.float32) for stem, _ in self.pieces]
             self.bias = (torch.cat(bs, dim=0) if len(bs) > 1 else bs[0]).contiguous()
 
     def bind_tensor(self, weight: torch.Tensor) -> None:

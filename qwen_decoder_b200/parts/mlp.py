@@ -4,7 +4,7 @@ W1 = gate_proj, W3 = up_proj, W2 = down_proj).  Gate and up are one stacked prod
 """
 from __future__ import annotations
 
-from typing import List
+from typing import List, Sequence
 
 import torch
 
@@ -18,12 +18,17 @@ from .linear import Linear
 
 @register_part("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
-    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "mlp."):
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "mlp.",
+                 names: Sequence[str] = ("gate_proj", "up_proj", "down_proj"), weight_suffix: str = ".weight"):
+        """``names``: what the gate, up and down matrices are called after ``prefix``."""
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
-        self.gate_up = Linear(hidden_size, [(f"{prefix}gate_proj", intermediate_size),
-                                            (f"{prefix}up_proj", intermediate_size)], bias=False)
-        self.down = Linear(intermediate_size, [(f"{prefix}down_proj", hidden_size)], bias=False)
+        g, u, d = names
+        self.gate_up = Linear(hidden_size, [(f"{prefix}{g}", intermediate_size),
+                                            (f"{prefix}{u}", intermediate_size)], bias=False,
+                              weight_suffix=weight_suffix)
+        self.down = Linear(intermediate_size, [(f"{prefix}{d}", hidden_size)], bias=False,
+                           weight_suffix=weight_suffix)
         self._barrier = None
 
     def tensor_specs(self) -> List[TensorSpec]:

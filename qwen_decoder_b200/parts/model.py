@@ -22,6 +22,7 @@ from .base import PagedCacheView, ResidualStream, StateCacheView
 from .linear import Linear
 # importing the part modules registers them
 from . import attention as _attention, block as _block, mlp as _mlp, norm as _norm, rotary as _rotary  # noqa: F401
+from . import latent_attention as _latent, mamba2 as _mamba2, moe as _moe  # noqa: F401
 
 
 class DecoderModel:
@@ -42,15 +43,20 @@ class DecoderModel:
                     raise ValueError(f"layer {ls.prefix!r}: unknown position encoding {pname!r}")
                 mp["position"] = self.positions[pname] if pname is not None else None
             mixer = create_part("mixer", ls.mixer.name, **mp)
-            fp = dict(ls.feed_forward.params)
-            fp["prefix"] = ls.prefix + fp.get("prefix", "")
-            ff = create_part("feed_forward", ls.feed_forward.name, **fp)
+            ff = None
+            if ls.feed_forward is not None:
+                fp = dict(ls.feed_forward.params)
+                fp["prefix"] = ls.prefix + fp.get("prefix", "")
+                ff = create_part("feed_forward", ls.feed_forward.name, **fp)
             norms = {}
             for role, ns in ls.norms.items():
                 np_ = dict(ns.params)
                 np_["prefix"] = ls.prefix + np_.get("prefix", "")
                 norms[role] = create_part("norm", ns.name, **np_)
-            self.layers.append(create_part("block", ls.block, mixer=mixer, feed_forward=ff, norms=norms))
+            bp = dict(ls.block_params)
+            if "prefix" in bp:
+                bp["prefix"] = ls.prefix + bp["prefix"]
+            self.layers.append(create_part("block", ls.block, mixer=mixer, feed_forward=ff, norms=norms, **bp))
         for i, e in enumerate(spec.schedule):
             if not (0 <= e.layer < len(self.layers)):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.layers)}")
@@ -58,9 +64,14 @@ class DecoderModel:
         fn = dict(spec.final_norm.params)
         fn["prefix"] = spec.final_norm_prefix + fn.get("prefix", "")
         self.final_norm = create_part("norm", spec.final_norm.name, **fn)
-        self.lm_head = Linear(spec.hidden_size, [("lm_head", spec.vocab_size)], bias=False) \
-            if spec.lm_head_tensor is None else \
-            Linear(spec.hidden_size, [(spec.lm_head_tensor[:-len(".weight")], spec.vocab_size)], bias=False)
+        head = spec.lm_head_tensor
+        if head is None:
+            self.lm_head = Linear(spec.hidden_size, [("lm_head", spec.vocab_size)], bias=False)
+        elif head.endswith(".weight"):
+            self.lm_head = Linear(spec.hidden_size, [(head[:-len(".weight")], spec.vocab_size)], bias=False)
+        else:           # a model that names its output matrix without the suffix
+            self.lm_head = Linear(spec.hidden_size, [(head, spec.vocab_size)], bias=False, weight_suffix="")
+        self.embedding_scale = float(spec.embedding_scale)
         self.embedding: Optional[torch.Tensor] = None
         self.native_prompt = None    # parts.native_prompt.NativePrompt once bound, if the parts allow it
         self.dtype: Optional[torch.dtype] = None
@@ -128,7 +139,7 @@ class DecoderModel:
     def forward(self, ctx) -> torch.Tensor:
         """Run the step's tokens through the model; float32 logits [n_wanted, vocab]."""
         x = torch.empty((ctx.num_tokens, self.hidden_size), dtype=torch.float32, device=self.device)
-        kernels.embedding(x, self.embedding, ctx.tokens)
+        kernels.embedding(x, self.embedding, ctx.tokens, self.embedding_scale)
         if self.native_prompt is not None and self.native_prompt.takes(ctx):
             # the common composition, many tokens: the layers' launches come from one native loop
             h = self.native_prompt.forward(ctx, x)

@@ -19,18 +19,24 @@ from .base import Norm, ResidualStream
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
-    def __init__(self, size: int, eps: float, prefix: str = ""):
+    def __init__(self, size: int, eps: float, prefix: str = "", tensor: str = "weight", offset: float = 0.0):
+        """``tensor``: the scale's name after ``prefix``.  ``offset``: the stored scale is kept around
+        ``-offset`` and the norm multiplies by ``offset + w`` (1 for scales stored around zero)."""
         self.size = size
         self.eps = float(eps)
         self.prefix = prefix
+        self.tensor = tensor
+        self.offset = float(offset)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(f"{self.prefix}weight", (self.size,), init="around_one")]
+        return [TensorSpec(f"{self.prefix}{self.tensor}", (self.size,),
+                           init="around_one" if self.offset == 0.0 else "around_zero")]
 
     def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
-        # norm scales are used in float32 whatever they are stored in
-        self.weight = source.get(f"{self.prefix}weight").to(device=device, dtype=torch.float32).contiguous()
+        # norm scales are used in float32 whatever they are stored in; the offset is added once, here
+        w = source.get(f"{self.prefix}{self.tensor}").to(device=device, dtype=torch.float32)
+        self.weight = (w + self.offset if self.offset != 0.0 else w).contiguous()
 
     def native_params(self) -> Optional[dict]:
         return {"kind": "rmsnorm", "weight": self.weight, "eps": self.eps, "size": self.size}
@@ -40,7 +46,8 @@ class RMSNorm(Norm):
         n = stream.x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.size), dtype=out_dtype, device=stream.x.device)
         kernels.add_rmsnorm(stream.x, stream.delta, self.weight, out, self.eps, rows=rows,
-                            write_back=rows is None)
+                            write_back=rows is None, delta_scale=stream.delta_scale)
         if rows is None:
             stream.delta = None
+            stream.delta_scale = None
         return out

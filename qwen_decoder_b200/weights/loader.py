@@ -36,7 +36,8 @@ class WeightError(ValueError):
 @dataclass(frozen=True)
 class TensorSpec:
     """A tensor a part needs: full name, shape, and how random weights fill it
-    (``normal``: N(0, std); ``around_one``: 1 + N(0, norm_std), for norm scales)."""
+    (``normal``: N(0, std); ``around_one``: 1 + N(0, norm_std), for norm scales; ``around_zero``: N(0, norm_std),
+    for scales stored as their distance from one; ``uniform:lo:hi``)."""
     name: str
     shape: Tuple[int, ...]
     init: str = "normal"

@@ -30,6 +30,11 @@ def random_tensor(spec: TensorSpec, seed: int, dtype=torch.bfloat16, device="cpu
     t = torch.empty(spec.shape, dtype=torch.float32, device=device)
     if spec.init == "around_one":
         t.normal_(0.0, norm_std, generator=g).add_(1.0)
+    elif spec.init == "around_zero":
+        t.normal_(0.0, norm_std, generator=g)
+    elif spec.init.startswith("uniform:"):          # "uniform:lo:hi"
+        lo, hi = (float(v) for v in spec.init.split(":")[1:3])
+        t.uniform_(lo, hi, generator=g)
     else:
         t.normal_(0.0, std, generator=g)
     return t.to(dtype)
