@@ -229,7 +229,146 @@ def mixed_step(args):
     return 0
 
 
+# ---- the hybrid design beside the dense decoder at equal layer sizes -------------------------------------------
+# Sizes that resemble real models' layers.  Per size: the hybrid (state-space and latent-attention layers in turn, dense
+# and routed feed-forwards in turn) and the dense decoder with the same width, layer count, dense feed-forward and vocabulary.
+HYBRID_SIZES = {
+    "S": dict(width=2048, vocab=32000, repeats=2, ff=5632,
+              mamba=dict(heads=64, vdim=64, state=128, groups=8, conv=4, norm_groups=8),
+              latent=dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1536),
+              moe=dict(experts=64, top=6, ff=1408, shared=2816), dense_heads=(16, 2)),
+    "M": dict(width=4096, vocab=32000, repeats=2, ff=11008,
+              mamba=dict(heads=128, vdim=64, state=128, groups=8, conv=4, norm_groups=8),
+              latent=dict(heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1536),
+              moe=dict(experts=32, top=4, ff=2048, shared=4096), dense_heads=(32, 8)),
+}
+
+
+def hybrid_configs(size):
+    from qwen_decoder_b200.config import config_from_dict
+    z = HYBRID_SIZES[size]
+    lat = dict(z["latent"], rot={"base": 10000.0, "dims": z["latent"]["rot_dim"]},
+               scale=(z["latent"]["dim"] + z["latent"]["rot_dim"]) ** -0.5)
+    moe = {"kind": "moe", "expert": {"ff": z["moe"]["ff"]}, "router": {"experts": z["moe"]["experts"], "top": z["moe"]["top"]},
+           "shared": {"ff": z["moe"]["shared"]}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    layers = []
+    for _ in range(z["repeats"]):
+        layers += [{"type": "mamba2", "mixer": z["mamba"], "mlp": dense}, {"type": "mamba2", "mixer": z["mamba"], "mlp": moe},
+                   {"type": "latent_attention", "mixer": lat, "mlp": dense}, {"type": "latent_attention", "mixer": lat, "mlp": moe}]
+    hybrid = config_from_dict({"architecture": "Zunuvik", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0},
+                               "norm": {"eps": 1e-6}, "layers": layers})
+    H, G = z["dense_heads"]
+    dense_cfg = config_from_dict(dict(
+        architectures=["Qwen2ForCausalLM"], hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=len(layers),
+        num_attention_heads=H, num_key_value_heads=G, head_dim=128, vocab_size=z["vocab"], max_position_embeddings=32768,
+        rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False))
+    return hybrid, dense_cfg
+
+
+def hybrid_bench(args):
+    """``--micro hybrid``: decode steps (batch 1, 8, 64 at ``--context``) and a prompt of ``--prefill-tokens`` tokens, for the
+    hybrid design and for the dense decoder at equal sizes; one JSON line.  ``--only hybrid|dense`` and ``--phase`` narrow it
+    (for a launch list under a profiler)."""
+    import torch
+    from qwen_decoder_b200 import kernels
+    from qwen_decoder_b200.engine import ModelRunner, StepEntry
+    W, K = max(3, args.warmup), max(1, min(args.steps, 64))
+    page, ctxlen, T = args.page_size, args.context, args.prefill_tokens
+    batches = [int(b) for b in args.points.split(",") if b] if args.phase != "prefill" else []
+    if args.phase in ("all", "decode") and args.batch not in batches:
+        batches = sorted(set(batches + [args.batch]))
+    out = {"micro": "hybrid", "size": args.hybrid_size, "context": ctxlen, "prefill_tokens": T, "dtype": "bf16",
+           "data": "synthetic: random weights, random token ids, random cache contents", "models": {}}
+    gen = torch.Generator().manual_seed(1)
+    clocks = ClockSampler()
+    clocks.start()
+    for name, cfg in zip(("hybrid", "dense"), hybrid_configs(args.hybrid_size)):
+        if args.only and args.only != name:
+            continue
+        max_b = max(batches + [1])
+        span = ctxlen + 2 * (W + K) + 64
+        pages = max(max_b * ((span + page - 1) // page), (T + page - 1) // page) + 64
+        runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", num_pages=pages, page_size=page,
+                                         max_requests=max_b, max_positions=max(span, T) + 64)
+        dev = runner.device
+        for kv in runner.cache.kv:
+            kv.normal_(0.0, 1.0)
+        res = {}
+        for b in batches:
+            rcs = []
+            for i in range(b):
+                rc = runner.open(f"{name}{b}_{i}")
+                runner.cache.ensure(rc, ctxlen)
+                runner.cache.commit(rc, ctxlen)
+                rcs.append(rc)
+            toks = torch.randint(0, cfg.vocab_size, (W + K, b), generator=gen).tolist()
+            for i in range(W):
+                runner.step([StepEntry(rc, [toks[i][j]], [0]) for j, rc in enumerate(rcs)])
+            torch.cuda.synchronize(dev)
+            l0 = kernels.launches()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(W, W + K):
+                runner.step([StepEntry(rc, [toks[i][j]], [0]) for j, rc in enumerate(rcs)])
+            e1.record()
+            torch.cuda.synchronize(dev)
+            ms = e0.elapsed_time(e1) / K
+            res[f"decode_b{b}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(b / ms * 1e3, 1),
+                                   "launches_per_step": (kernels.launches() - l0) // K}
+            for rc in rcs:
+                runner.close(rc)
+        if args.phase in ("all", "prefill"):
+            times = []
+            for i in range(W + 3):
+                rc = runner.open(f"{name}p{i}")
+                prompt = torch.randint(0, cfg.vocab_size, (T,), generator=gen).tolist()
+                torch.cuda.synchronize(dev)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                runner.step([StepEntry(rc, prompt, [T - 1])])
+                e1.record()
+                torch.cuda.synchronize(dev)
+                if i >= W:
+                    times.append(e0.elapsed_time(e1))
+                runner.close(rc)
+            ms = sorted(times)[len(times) // 2]
+            res["prefill"] = {"ms": round(ms, 3), "tokens_per_s": round(T / ms * 1e3, 1)}
+        res["weight_gb"] = round(sum(t.numel() * t.element_size() for t in _model_tensors(runner.model)) / 1e9, 3)
+        out["models"][name] = res
+        del runner
+        torch.cuda.empty_cache()
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
+def _model_tensors(model):
+    import torch
+    seen, out = set(), []
+
+    def walk(o, depth=0):
+        if isinstance(o, torch.Tensor):
+            if o.is_cuda and o.data_ptr() not in seen:
+                seen.add(o.data_ptr())
+                out.append(o)
+        elif depth < 5 and hasattr(o, "__dict__") and not isinstance(o, type):
+            for k, v in vars(o).items():
+                if k not in ("position", "positions", "native_prompt", "spec"):
+                    walk(v, depth + 1)
+        elif depth < 5 and isinstance(o, (list, tuple)):
+            for v in o:
+                walk(v, depth + 1)
+        elif depth < 5 and isinstance(o, dict):
+            for v in o.values():
+                walk(v, depth + 1)
+    walk(model)
+    return out
+
+
 def micro(args):
+    if args.micro == "hybrid":
+        return hybrid_bench(args)
     """One kernel alone: W-streaming contraction, decode attention or prefill attention at the 3B sizes."""
     if args.micro == "serve":
         return serve(args)
@@ -479,7 +618,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--timeline", action="store_true",
                     help="with --micro prefill_attention: print the kernel's own time stamps of one CTA (microseconds) to stderr")
-    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention", "serve", "mixed_step"],
+    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention", "serve", "mixed_step", "hybrid"],
                     help="time one kernel alone at the 3B shape (for profiles/), or with 'serve' a whole run of "
                          "--batch requests (--context prompt tokens, --steps new tokens each) through the entry "
                          "point; print one JSON line and exit")
@@ -491,6 +630,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--micro-graph", action="store_true", help="gemm: time inside a replayed graph, cold weights")
     ap.add_argument("--micro-splits", type=int, default=1, help="gemm with --micro-graph: shares of K (partial sums)")
+    ap.add_argument("--hybrid-size", default="S", choices=["S", "M"], help="hybrid: which layer sizes")
+    ap.add_argument("--only", default=None, choices=["hybrid", "dense"], help="hybrid: one of the two models")
+    ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill"], help="hybrid: decode steps, the prompt, or both")
     ap.add_argument("--history", type=int, default=2048, help="mixed_step: cached tokens before the prompt portion")
     ap.add_argument("--stamps", action="store_true",
                     help="for profiles/: run the decode step (up to 8 requests) with the attention and feed-forward "

@@ -77,7 +77,7 @@ latent_absorb_kernel(const float* __restrict__ q, const TW* __restrict__ wuk, fl
     qs[i] = tt < nt ? q[(size_t)(t0 + tt) * qw + (size_t)h * (dn + dr) + d] : 0.f;
   }
   __syncthreads();
-  for (int j = threadIdx.x; j < r; j += blockDim.x) {
+  for (int j = blockIdx.z * blockDim.x + threadIdx.x; j < r; j += gridDim.z * blockDim.x) {
     float acc[LA_TT];
 #pragma unroll
     for (int tt = 0; tt < LA_TT; tt++) acc[tt] = 0.f;
@@ -91,6 +91,7 @@ latent_absorb_kernel(const float* __restrict__ q, const TW* __restrict__ wuk, fl
     for (int tt = 0; tt < LA_TT; tt++)
       if (tt < nt) qcat[((size_t)(t0 + tt) * H + h) * W + j] = acc[tt];
   }
+  if (blockIdx.z != 0) return;
   const int half = rot_dims >> 1;
   for (int i = threadIdx.x; i < nt * dr; i += blockDim.x) {
     int tt = i / dr, e = i - tt * dr;
@@ -230,7 +231,7 @@ __global__ void latent_combine_kernel(const float* __restrict__ part_o, const fl
 
 // ----------------------------------------------------------------------------- expand
 // out[t, h * dv + i] = (sum_j Wuv[h * dv + i, j] o_lat[t, h, j]) * sigmoid(gate[t, h * dv + i]); gate float32 with
-// row stride ldg (null: no gate).  A warp per output row of Wuv, LA_TT tokens a CTA.
+// row stride ldg (null: no gate).  A warp per output row of Wuv, LA_TT tokens and 32 output rows a CTA.
 template <typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 latent_expand_kernel(const float* __restrict__ o_lat, const TW* __restrict__ wuv, const float* __restrict__ gate,
@@ -246,7 +247,8 @@ latent_expand_kernel(const float* __restrict__ o_lat, const TW* __restrict__ wuv
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int i = warp; i < dv; i += nw) {
+  const int i_hi = min(dv, (int)(blockIdx.z + 1) * 32);
+  for (int i = blockIdx.z * 32 + warp; i < i_hi; i += nw) {
     const TW* wrow = wuv + ((size_t)h * dv + i) * r;
     float acc[LA_TT];
 #pragma unroll
@@ -297,7 +299,7 @@ extern "C" int qd_latent_absorb(const float* q, const void* wuk, int w_dtype, fl
   if (T <= 0) return 0;
   size_t smem = (size_t)LA_TT * dn * sizeof(float);
   if (smem > 48 * 1024 || H > 65535) return QD_ERR_UNSUPPORTED;
-  dim3 grid((T + LA_TT - 1) / LA_TT, H);
+  dim3 grid((T + LA_TT - 1) / LA_TT, H, (r + 255) / 256);
   if (w_dtype == QD_F32)
     qd_launch(latent_absorb_kernel<float>, grid, dim3(256), smem, stream, q, (const float*)wuk, qcat, T, H, dn, dr, r,
               cos_t, sin_t, rot_dims, positions);
@@ -342,7 +344,7 @@ extern "C" int qd_latent_expand(const float* o_lat, const void* wuv, int w_dtype
   if (T <= 0) return 0;
   size_t smem = (size_t)LA_TT * r * sizeof(float);
   if (smem > 48 * 1024 || H > 65535) return QD_ERR_UNSUPPORTED;
-  dim3 grid((T + LA_TT - 1) / LA_TT, H);
+  dim3 grid((T + LA_TT - 1) / LA_TT, H, (dv + 31) / 32);
   if (w_dtype == QD_F32 && out_dtype == QD_F32)
     qd_launch(latent_expand_kernel<float, float>, grid, dim3(256), smem, stream, o_lat, (const float*)wuv, gate, ldg,
               (float*)out, T, H, dv, r);

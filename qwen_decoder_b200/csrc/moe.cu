@@ -16,50 +16,98 @@
 #define MOE_MAX_TOP 32
 
 // ----------------------------------------------------------------------------- route
-template <typename T>
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const T* __restrict__ h, const T* __restrict__ wr, const float* __restrict__ br,
-                 const T* __restrict__ wsg, int n_tokens, int D, int E, int top, int* __restrict__ idx,
-                 float* __restrict__ wt, float* __restrict__ sgate) {
+// 16 bytes of a row as floats (8 bfloat16 or 4 float32)
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  __device__ static void load(const float* p, float* o) { float4 v = *reinterpret_cast<const float4*>(p); o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; }
+};
+template <> struct Vec16<bf16> {
+  static constexpr int N = 8;
+  __device__ static void load(const bf16* p, float* o) {
+    uint4 v = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) { o[2 * i] = __low2float(h[i]); o[2 * i + 1] = __high2float(h[i]); }
+  }
+};
+
+#define MR_TOKENS 8
+// logits[t, e] = wr[e] . h[t] + br[e] in float32; row E of the output (when wsg is given) is sigmoid(wsg . h[t]).
+// grid (token tiles of MR_TOKENS, groups of 8 rows of wr): a warp owns one row of wr and reads it once for the tile.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+moe_logits_kernel(const T* __restrict__ h, const T* __restrict__ wr, const float* __restrict__ br,
+                  const T* __restrict__ wsg, int n_tokens, int D, int E, float* __restrict__ logits,
+                  float* __restrict__ sgate) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float lg[];                 // [warps][E]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (t >= n_tokens) return;
-  float* my = lg + (size_t)warp * E;
-  const T* x = h + (size_t)t * D;
-  for (int e = 0; e < E; e++) {
-    float acc = 0.f;
-    for (int i = lane; i < D; i += 32) acc = fmaf(to_float(x[i]), to_float(wr[(size_t)e * D + i]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) my[e] = acc + br[e];
-  }
-  if (wsg) {
-    float acc = 0.f;
-    for (int i = lane; i < D; i += 32) acc = fmaf(to_float(x[i]), to_float(wsg[i]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) sgate[t] = 1.0f / (1.0f + expf(-acc));
-  }
-  __syncwarp();
-  if (lane == 0) {
-    float v[MOE_MAX_TOP];
-    for (int k = 0; k < top; k++) {
-      int best = -1;
-      float bv = -INFINITY;
-      for (int e = 0; e < E; e++) {
-        float z = my[e];
-        if (best < 0 || z > bv) { best = e; bv = z; }
+  const int e = blockIdx.y * 8 + warp, t0 = blockIdx.x * MR_TOKENS;
+  const int rows = E + (wsg ? 1 : 0);
+  if (e >= rows) return;
+  const T* w = e < E ? wr + (size_t)e * D : wsg;
+  const int nt = min(MR_TOKENS, n_tokens - t0);
+  float acc[MR_TOKENS];
+#pragma unroll
+  for (int i = 0; i < MR_TOKENS; i++) acc[i] = 0.f;
+  if (VEC) {
+    constexpr int V = Vec16<T>::N;
+    for (int k = lane * V; k < D; k += 32 * V) {
+      float wv[V], xv[V];
+      Vec16<T>::load(w + k, wv);
+#pragma unroll
+      for (int i = 0; i < MR_TOKENS; i++) {
+        if (i < nt) {
+          Vec16<T>::load(h + (size_t)(t0 + i) * D + k, xv);
+#pragma unroll
+          for (int j = 0; j < V; j++) acc[i] = fmaf(xv[j], wv[j], acc[i]);
+        }
       }
-      idx[(size_t)t * top + k] = best;
-      v[k] = bv;
-      my[best] = -INFINITY;
     }
-    float sum = 0.f;
-    const float vmax = v[0];                      // the first chosen is the largest
-    for (int k = 0; k < top; k++) { v[k] = expf(v[k] - vmax); sum += v[k]; }
-    for (int k = 0; k < top; k++) wt[(size_t)t * top + k] = v[k] / sum;
+  } else {
+    for (int k = lane; k < D; k += 32) {
+      float wv = to_float(w[k]);
+#pragma unroll
+      for (int i = 0; i < MR_TOKENS; i++)
+        if (i < nt) acc[i] = fmaf(to_float(h[(size_t)(t0 + i) * D + k]), wv, acc[i]);
+    }
   }
+#pragma unroll
+  for (int i = 0; i < MR_TOKENS; i++) {
+    float v = warp_sum(acc[i]);
+    if (lane == 0 && i < nt) {
+      if (e < E) logits[(size_t)(t0 + i) * E + e] = v + br[e];
+      else sgate[t0 + i] = 1.0f / (1.0f + expf(-v));
+    }
+  }
+}
+
+// One thread per token: the ``top`` largest logits (the lower index wins a tie) and the softmax over them.
+__global__ void __launch_bounds__(128)
+moe_topk_kernel(float* __restrict__ logits, int n_tokens, int E, int top, int* __restrict__ idx,
+                float* __restrict__ wt) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_tokens) return;
+  float* my = logits + (size_t)t * E;
+  float v[MOE_MAX_TOP];
+  for (int k = 0; k < top; k++) {
+    int best = -1;
+    float bv = -INFINITY;
+    for (int e = 0; e < E; e++) {
+      float z = my[e];
+      if (best < 0 || z > bv) { best = e; bv = z; }
+    }
+    idx[(size_t)t * top + k] = best;
+    v[k] = bv;
+    my[best] = -INFINITY;
+  }
+  float sum = 0.f;
+  const float vmax = v[0];                        // the first chosen is the largest
+  for (int k = 0; k < top; k++) { v[k] = expf(v[k] - vmax); sum += v[k]; }
+  for (int k = 0; k < top; k++) wt[(size_t)t * top + k] = v[k] / sum;
 }
 
 // ----------------------------------------------------------------------------- sort
@@ -175,6 +223,165 @@ moe_gemm_kernel(const TI* __restrict__ A, long long lda, const int* __restrict__
   }
 }
 
+// ----------------------------------------------------------------------------- few rows per expert
+// While an expert sees at most MG_ROWS pairs of a step (decoding), its weights are what the step reads: a warp
+// owns output rows of the expert's matrix, reads each once in 16-byte pieces, and multiplies it with the tile's
+// rows, which lie in shared memory.  grid (ceil(N / 64), tiles).
+#define MG_ROWS 8
+template <typename TI, typename TW, typename TO, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_gemv_kernel(const TI* __restrict__ A, long long lda, const int* __restrict__ pair_at, int top, int by_token,
+                const TW* __restrict__ W1, const TW* __restrict__ W2, TO* __restrict__ out, int N, int K,
+                const int* __restrict__ meta, int E) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if ((int)blockIdx.y >= meta[E + 1]) return;
+  const int* tile = meta + E + 2 + 3 * blockIdx.y;
+  const int e = tile[0], row0 = tile[1], rows = tile[2];
+  extern __shared__ __align__(16) unsigned char mg_raw[];
+  TI* xs = reinterpret_cast<TI*>(mg_raw);        // [MG_ROWS][K]
+  constexpr int VI = Vec16<TI>::N;
+  for (int i = threadIdx.x * VI; i < rows * K; i += blockDim.x * VI) {
+    int r = i / K, k = i - r * K;
+    int src = by_token ? pair_at[row0 + r] / top : row0 + r;
+    *reinterpret_cast<uint4*>(xs + (size_t)r * K + k) = *reinterpret_cast<const uint4*>(A + (size_t)src * lda + k);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int V = Vec16<TW>::N;                // TI and TW are the same type in every instantiation
+  for (int i = 0; i < 8; i++) {
+    const int n = blockIdx.x * 64 + warp * 8 + i;
+    if (n >= N) break;
+    const TW* w1 = W1 + ((size_t)e * N + n) * K;
+    const TW* w2 = GATED ? W2 + ((size_t)e * N + n) * K : nullptr;
+    float a1[MG_ROWS], a2[MG_ROWS];
+#pragma unroll
+    for (int r = 0; r < MG_ROWS; r++) a1[r] = a2[r] = 0.f;
+    for (int k = lane * V; k < K; k += 32 * V) {
+      float w1v[V], w2v[V], xv[V];
+      Vec16<TW>::load(w1 + k, w1v);
+      if (GATED) Vec16<TW>::load(w2 + k, w2v);
+#pragma unroll
+      for (int r = 0; r < MG_ROWS; r++) {
+        if (r < rows) {
+          Vec16<TI>::load(xs + (size_t)r * K + k, xv);
+#pragma unroll
+          for (int j = 0; j < V; j++) {
+            a1[r] = fmaf(xv[j], w1v[j], a1[r]);
+            if (GATED) a2[r] = fmaf(xv[j], w2v[j], a2[r]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < MG_ROWS; r++) {
+      if (r < rows) {
+        float v = warp_sum(a1[r]);
+        if (GATED) v = v / (1.0f + expf(-v)) * warp_sum(a2[r]);
+        if (lane == 0) out[(size_t)(row0 + r) * N + n] = from_float<TO>(v);
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- many rows per expert, bfloat16
+// Tiles of 64 pairs x 64 output columns on the tensor cores (mma.sync m16n8k16, bfloat16 in, float32 sums), K in
+// steps of 32 through shared memory, the next step's 16-byte pieces fetched into registers while this one
+// multiplies.  Four warps, each 16 rows x 64 columns.  K must be a multiple of 8.
+__device__ __forceinline__ void mma_bf16_16816(float* c, const unsigned* a, const unsigned* b) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+#define MM_LD 40            // row pitch of a 32-element step in shared memory (bfloat16): no bank conflicts
+template <typename TO, bool GATED>
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ pair_at, int top, int by_token,
+                    const bf16* __restrict__ W1, const bf16* __restrict__ W2, TO* __restrict__ out, int N, int K,
+                    const int* __restrict__ meta, int E) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if ((int)blockIdx.y >= meta[E + 1]) return;
+  const int* tile = meta + E + 2 + 3 * blockIdx.y;
+  const int e = tile[0], row0 = tile[1], rows = tile[2];
+  __shared__ __align__(16) bf16 As[64 * MM_LD];
+  __shared__ __align__(16) bf16 B1[64 * MM_LD];
+  __shared__ __align__(16) bf16 B2[GATED ? 64 * MM_LD : 8];
+  __shared__ int src[64];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
+  const int n0 = blockIdx.x * 64;
+  if (tid < 64) src[tid] = tid < rows ? (by_token ? pair_at[row0 + tid] / top : row0 + tid) : -1;
+  __syncthreads();
+  const bf16* w1 = W1 + (size_t)e * N * K;
+  const bf16* w2 = GATED ? W2 + (size_t)e * N * K : nullptr;
+  // each thread moves two 16-byte pieces of each tile per step: piece p = tid + 128 * i -> row p / 4, k (p % 4) * 8
+  uint4 ra[2], rb1[2], rb2[2];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      int p = tid + 128 * i, row = p >> 2, k = k0 + (p & 3) * 8;
+      const uint4 zero = make_uint4(0, 0, 0, 0);
+      ra[i] = (src[row] >= 0 && k < K) ? *reinterpret_cast<const uint4*>(A + (size_t)src[row] * lda + k) : zero;
+      bool ok = n0 + row < N && k < K;
+      rb1[i] = ok ? *reinterpret_cast<const uint4*>(w1 + (size_t)(n0 + row) * K + k) : zero;
+      if (GATED) rb2[i] = ok ? *reinterpret_cast<const uint4*>(w2 + (size_t)(n0 + row) * K + k) : zero;
+    }
+  };
+  float c1[8][4], c2[GATED ? 8 : 1][4];
+#pragma unroll
+  for (int j = 0; j < 8; j++)
+#pragma unroll
+    for (int q = 0; q < 4; q++) { c1[j][q] = 0.f; if (GATED) c2[j][q] = 0.f; }
+  fetch(0);
+  for (int k0 = 0; k0 < K; k0 += 32) {
+    __syncthreads();                               // the step before has been read
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      int p = tid + 128 * i, row = p >> 2, kc = (p & 3) * 8;
+      *reinterpret_cast<uint4*>(As + row * MM_LD + kc) = ra[i];
+      *reinterpret_cast<uint4*>(B1 + row * MM_LD + kc) = rb1[i];
+      if (GATED) *reinterpret_cast<uint4*>(B2 + row * MM_LD + kc) = rb2[i];
+    }
+    __syncthreads();
+    if (k0 + 32 < K) fetch(k0 + 32);
+#pragma unroll
+    for (int ks = 0; ks < 32; ks += 16) {
+      unsigned a[4];
+      const bf16* ap = As + (warp * 16 + g) * MM_LD + ks + 2 * tq;
+      a[0] = *reinterpret_cast<const unsigned*>(ap);
+      a[1] = *reinterpret_cast<const unsigned*>(ap + 8 * MM_LD);
+      a[2] = *reinterpret_cast<const unsigned*>(ap + 8);
+      a[3] = *reinterpret_cast<const unsigned*>(ap + 8 * MM_LD + 8);
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        unsigned b[2];
+        const bf16* bp = B1 + (j * 8 + g) * MM_LD + ks + 2 * tq;
+        b[0] = *reinterpret_cast<const unsigned*>(bp);
+        b[1] = *reinterpret_cast<const unsigned*>(bp + 8);
+        mma_bf16_16816(c1[j], a, b);
+        if (GATED) {
+          const bf16* bq = B2 + (j * 8 + g) * MM_LD + ks + 2 * tq;
+          b[0] = *reinterpret_cast<const unsigned*>(bq);
+          b[1] = *reinterpret_cast<const unsigned*>(bq + 8);
+          mma_bf16_16816(c2[j], a, b);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; j++)
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      int r = warp * 16 + g + (q >> 1) * 8, n = n0 + j * 8 + 2 * tq + (q & 1);
+      if (r < rows && n < N) {
+        float v = c1[j][q];
+        if (GATED) v = v / (1.0f + expf(-v)) * c2[j][q];
+        out[(size_t)(row0 + r) * N + n] = from_float<TO>(v);
+      }
+    }
+}
+
 // ----------------------------------------------------------------------------- combine
 // out[t, :] = sum_k wt[t, k] * y[place[t * top + k], :] + sgate[t] * sum_p shared[p, t, :]   (float32 out)
 template <typename TS>
@@ -199,20 +406,23 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, c
 }
 
 // ----------------------------------------------------------------------------- launchers
+// logits: float32 scratch [T, E] (left with the chosen entries at -inf)
 extern "C" int qd_moe_route(const void* h, const void* wr, const float* br, const void* wsg, int dtype, int T, int D,
-                            int E, int top, int* idx, float* wt, float* sgate, cudaStream_t stream) {
+                            int E, int top, float* logits, int* idx, float* wt, float* sgate, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (top < 1 || top > E || top > MOE_MAX_TOP || E > 2048) return QD_ERR_UNSUPPORTED;
-  size_t smem = (size_t)4 * E * sizeof(float);
-  dim3 grid((T + 3) / 4);
-  if (dtype == QD_F32)
-    qd_launch(moe_route_kernel<float>, grid, dim3(128), smem, stream, (const float*)h, (const float*)wr, br,
-              (const float*)wsg, T, D, E, top, idx, wt, sgate);
-  else if (dtype == QD_BF16)
-    qd_launch(moe_route_kernel<bf16>, grid, dim3(128), smem, stream, (const bf16*)h, (const bf16*)wr, br,
-              (const bf16*)wsg, T, D, E, top, idx, wt, sgate);
-  else
-    return QD_ERR_UNSUPPORTED;
+  if (top < 1 || top > E || top > MOE_MAX_TOP) return QD_ERR_UNSUPPORTED;
+  const int rows = E + (wsg ? 1 : 0);
+  dim3 grid((T + MR_TOKENS - 1) / MR_TOKENS, (rows + 7) / 8);
+  if (grid.y > 65535) return QD_ERR_UNSUPPORTED;
+  const bool al = !(((uintptr_t)h | (uintptr_t)wr | (uintptr_t)wsg) & 15);
+#define MR_GO(T_, V_)                                                                                              \
+  qd_launch(moe_logits_kernel<T_, V_>, grid, dim3(256), 0, stream, (const T_*)h, (const T_*)wr, br, (const T_*)wsg, T, D, \
+            E, logits, sgate)
+  if (dtype == QD_F32) { if (al && D % 4 == 0) MR_GO(float, true); else MR_GO(float, false); }
+  else if (dtype == QD_BF16) { if (al && D % 8 == 0) MR_GO(bf16, true); else MR_GO(bf16, false); }
+  else return QD_ERR_UNSUPPORTED;
+#undef MR_GO
+  qd_launch(moe_topk_kernel, dim3((T + 127) / 128), dim3(128), 0, stream, logits, T, E, top, idx, wt);
   return qd_last_error();
 }
 
@@ -230,8 +440,41 @@ extern "C" int qd_moe_gemm(const void* A, long long lda, int a_dtype, const int*
                            const void* W1, const void* W2, int w_dtype, void* out, int out_dtype, int N, int K,
                            const int* meta, int E, int tile_rows, int max_tiles, int gated, cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
-  if (max_tiles > 65535 || (tile_rows != 16 && tile_rows != 64)) return QD_ERR_UNSUPPORTED;
+  if (max_tiles > 65535 || (tile_rows != 8 && tile_rows != 16 && tile_rows != 64)) return QD_ERR_UNSUPPORTED;
   dim3 grid((N + 63) / 64, max_tiles);
+  const bool al16 = !(((uintptr_t)A | (uintptr_t)W1 | (uintptr_t)W2) & 15);
+  if (tile_rows == 8) {
+    // few rows per expert: the weight-streaming kernel (16-byte pieces: K and the row pitch of A in whole pieces)
+    const int es = a_dtype == QD_F32 ? 4 : 2, per = 16 / es;
+    size_t smem = (size_t)MG_ROWS * K * es;
+    if (!al16 || K % per || lda % per || smem > 200 * 1024) return QD_ERR_UNSUPPORTED;
+#define MG_GO(TI, TW, TO, G)                                                                                         \
+  do {                                                                                                               \
+    if (smem > 48 * 1024)                                                                                            \
+      cudaFuncSetAttribute(moe_gemv_kernel<TI, TW, TO, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+    qd_launch(moe_gemv_kernel<TI, TW, TO, G>, grid, dim3(256), smem, stream, (const TI*)A, lda, pair_at, top, by_token, \
+              (const TW*)W1, (const TW*)W2, (TO*)out, N, K, meta, E);                                                \
+  } while (0)
+#define MG_PICK(TI, TW, TO) do { if (gated) MG_GO(TI, TW, TO, true); else MG_GO(TI, TW, TO, false); } while (0)
+    if (a_dtype == QD_F32 && w_dtype == QD_F32 && out_dtype == QD_F32) MG_PICK(float, float, float);
+    else if (a_dtype == QD_BF16 && w_dtype == QD_BF16 && out_dtype == QD_BF16) MG_PICK(bf16, bf16, bf16);
+    else if (a_dtype == QD_BF16 && w_dtype == QD_BF16 && out_dtype == QD_F32) MG_PICK(bf16, bf16, float);
+    else return QD_ERR_UNSUPPORTED;
+#undef MG_PICK
+#undef MG_GO
+    return qd_last_error();
+  }
+  if (tile_rows == 64 && a_dtype == QD_BF16 && w_dtype == QD_BF16 && al16 && K % 8 == 0 && lda % 8 == 0) {
+    // many rows per expert in bfloat16: tensor cores
+#define MM_GO(TO, G)                                                                                              \
+  qd_launch(moe_gemm_mma_kernel<TO, G>, grid, dim3(128), 0, stream, (const bf16*)A, lda, pair_at, top, by_token,  \
+            (const bf16*)W1, (const bf16*)W2, (TO*)out, N, K, meta, E)
+    if (out_dtype == QD_BF16) { if (gated) MM_GO(bf16, true); else MM_GO(bf16, false); }
+    else if (out_dtype == QD_F32) { if (gated) MM_GO(float, true); else MM_GO(float, false); }
+    else return QD_ERR_UNSUPPORTED;
+#undef MM_GO
+    return qd_last_error();
+  }
 #define MOE_GO(TI, TW, TO, TM, G)                                                                                   \
   qd_launch(moe_gemm_kernel<TI, TW, TO, TM, G>, grid, dim3(256), 0, stream, (const TI*)A, lda, pair_at, top, by_token, \
             (const TW*)W1, (const TW*)W2, (TO*)out, N, K, meta, E)

@@ -816,6 +816,18 @@ def mamba_gate_norm(y: torch.Tensor, u: torch.Tensor, z_off: int, w: torch.Tenso
 
 # ------------------------------------------------------------------ routed experts
 MOE_MAX_TOP = 32
+MOE_FEW_ROWS = 8          # rows of one expert that the weight-streaming grouped product takes as one tile
+
+
+def moe_tile_rows(n_pairs: int, E: int, K1: int, K2: int, dtype: torch.dtype) -> int:
+    """Rows of one expert per CTA in the grouped products: 8 (each expert's weights streamed once past its few
+    rows) while experts see about that many pairs or fewer, 64 (tensor-core tiles in bfloat16) when they see
+    many, 16 otherwise and wherever the faster forms' 16-byte pieces do not fit."""
+    per = 4 if dtype == torch.float32 else 8
+    pieces_fit = K1 % per == 0 and K2 % per == 0
+    if n_pairs <= MOE_FEW_ROWS * E and pieces_fit and MOE_FEW_ROWS * max(K1, K2) * (16 // per) <= 200 * 1024:
+        return MOE_FEW_ROWS
+    return 64 if n_pairs >= 32 * E else 16
 
 
 def moe_route(h: torch.Tensor, wr: torch.Tensor, br: torch.Tensor, wsg: Optional[torch.Tensor], top: int,
@@ -827,8 +839,11 @@ def moe_route(h: torch.Tensor, wr: torch.Tensor, br: torch.Tensor, wsg: Optional
     assert wr.shape == (E, D) and wr.dtype == h.dtype and br.dtype == torch.float32 and br.numel() == E
     assert idx.dtype == torch.int32 and wt.dtype == torch.float32 and idx.shape == wt.shape == (T, top)
     _contig(h, "h"); _contig(wr, "wr")
+    logits = torch.empty((T, E), dtype=torch.float32, device=h.device)
     _check(library("moe").qd_moe_route(_ptr(h), _ptr(wr), _ptr(br), _ptr(wsg), _I(dtype_code(h.dtype)), _I(T), _I(D),
-                                       _I(E), _I(top), _ptr(idx), _ptr(wt), _ptr(sgate), _stream()), "moe_route")
+                                       _I(E), _I(top), _ptr(logits), _ptr(idx), _ptr(wt), _ptr(sgate), _stream()),
+           "moe_route")
+    _launch_count[0] += 1
 
 
 def moe_sort(idx: torch.Tensor, E: int, tile_rows: int, max_tiles: int, place: torch.Tensor, pair_at: torch.Tensor,

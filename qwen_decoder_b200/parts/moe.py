@@ -70,7 +70,7 @@ class RoutedExperts(FeedForward):
         wt = torch.empty((T, top), dtype=torch.float32, device=dev)
         sgate = torch.empty((T,), dtype=torch.float32, device=dev) if self.shared is not None else None
         kernels.moe_route(x, self.w_router, self.b_router, self.w_sg, top, idx, wt, sgate)
-        tile_rows = 64 if n >= 32 * E else 16       # rows of one expert a CTA takes: small while experts see few tokens
+        tile_rows = kernels.moe_tile_rows(n, E, D, F, x.dtype)   # rows of one expert a CTA takes
         max_tiles = n // tile_rows + E              # sum over experts of ceil(count / tile_rows) is at most this
         place = torch.empty((n,), dtype=torch.int32, device=dev)
         pair_at = torch.empty((n,), dtype=torch.int32, device=dev)
