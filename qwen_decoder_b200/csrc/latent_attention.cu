@@ -206,6 +206,200 @@ latent_attend_kernel(const float* __restrict__ qcat, const TC* __restrict__ cach
   }
 }
 
+// ----------------------------------------------------------------------------- attend on tensor cores (bfloat16)
+// grid (tokens, groups of 16 heads, splits); 8 warps.  The 16 heads of a token are the rows of one m16 tile: they
+// share the token's keys, so one staged tile of 64 cached rows serves all of them.  Per key tile:
+//   S = Q K^T      warp w takes keys 8w .. 8w+7 (one n-tile), K-dimension the whole row (latent + rotated part);
+//                  the float32 queries enter as TWO bfloat16 numbers, q = hi + lo (two products, one sum)
+//   softmax        float32 on S in shared memory; the weights leave as TWO bfloat16 numbers, p = hi + lo, so that
+//                  the product with the values sees them to 16 bits of mantissa, not 8
+//   O += P V       V is the latent part of the same staged rows (ldmatrix.trans); warp w owns columns 8j, j = w mod 8
+// The next tile's rows travel by cp.async into the other buffer meanwhile; keys outside the token's range arrive
+// as zeros (a copy of zero bytes).  Needs the row and the latent to be whole 16-byte pieces (multiples of 8).
+#define LM_KT 64
+__device__ __forceinline__ void lm_mma(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(256)
+latent_attend_mma_kernel(const float* __restrict__ qcat, const bf16* __restrict__ cache,
+                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ token_req,
+                         const int* __restrict__ positions, int H, int r, int dr, int page_size, float scale, int window,
+                         int splits, float* __restrict__ o_lat, float* __restrict__ part_o,
+                         float* __restrict__ part_ml) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) unsigned char lm_raw[];
+  const int W = r + dr, Wq = (W + 15) & ~15, P = Wq + 8;         // pitch of a staged row in elements
+  bf16* Qs = reinterpret_cast<bf16*>(lm_raw);                    // [16][P]: the queries' leading 8 bits of mantissa
+  bf16* Ql = Qs + 16 * P;                                        // [16][P]: what those left out (q = hi + lo)
+  bf16* Ks = Ql + 16 * P;                                        // [2][LM_KT][P]
+  float* Ss = reinterpret_cast<float*>(Ks + 2 * LM_KT * P);      // [16][68]
+  bf16* Ph = reinterpret_cast<bf16*>(Ss + 16 * 68);              // [16][72]
+  bf16* Pl = Ph + 16 * 72;                                       // [16][72]
+  float* m_s = reinterpret_cast<float*>(Pl + 16 * 72);           // [16]
+  float* l_s = m_s + 16;
+  float* corr_s = l_s + 16;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
+  const int t = blockIdx.x, h0 = blockIdx.y * 16, split = blockIdx.z;
+  const int pos = positions[t];
+  const int* bt = block_table + (size_t)token_req[t] * max_blocks;
+  const int key_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int tile_lo = key_lo / LM_KT, n_tiles = pos / LM_KT + 1 - tile_lo;
+  const int my_lo = tile_lo + (int)((long long)n_tiles * split / splits);
+  const int my_hi = tile_lo + (int)((long long)n_tiles * (split + 1) / splits);
+  const int pieces = W >> 3;                                     // 16-byte pieces of a cached row
+
+  auto issue = [&](int tile, int buf) {
+    bf16* dst = Ks + (size_t)buf * LM_KT * P;
+    for (int p = tid; p < LM_KT * pieces; p += 256) {
+      int row = p / pieces, c = p - row * pieces, key = tile * LM_KT + row;
+      bool ok = key >= key_lo && key <= pos;
+      const bf16* src = ok ? cache + ((size_t)bt[key / page_size] * page_size + key % page_size) * W + c * 8 : cache;
+      unsigned d = (unsigned)__cvta_generic_to_shared(dst + row * P + c * 8);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(ok ? 16 : 0) : "memory");
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+
+  for (int i = tid; i < 16 * Wq; i += 256) {
+    int row = i / Wq, e = i - row * Wq;
+    float v = (h0 + row < H && e < W) ? qcat[((size_t)t * H + h0 + row) * W + e] : 0.f;
+    bf16 hi = __float2bfloat16_rn(v);
+    Qs[row * P + e] = hi;
+    Ql[row * P + e] = __float2bfloat16_rn(v - __bfloat162float(hi));
+  }
+  if (Wq > W)
+    for (int i = tid; i < 2 * LM_KT * (Wq - W); i += 256) {
+      int row = i / (Wq - W), e = W + i - row * (Wq - W);
+      Ks[row * P + e] = __float2bfloat16_rn(0.f);
+    }
+  if (tid < 16) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; }
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+#pragma unroll
+    for (int q = 0; q < 4; q++) acc[i][q] = 0.f;
+  const int n_ntiles = r >> 3;                                   // n-tiles of 8 latent columns; warp w owns w, w + 8, ...
+
+  if (my_lo < my_hi) issue(my_lo, 0);
+  for (int tile = my_lo; tile < my_hi; tile++) {
+    const int buf = (tile - my_lo) & 1;
+    if (tile + 1 < my_hi) {
+      issue(tile + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    }
+    __syncthreads();
+    const bf16* Kb = Ks + (size_t)buf * LM_KT * P;
+    {   // S = Q K^T for this warp's 8 keys
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      const bf16* qa = Qs + g * P + 2 * tq;
+      const bf16* ql = Ql + g * P + 2 * tq;
+      const bf16* kb = Kb + (warp * 8 + g) * P + 2 * tq;
+      for (int ks = 0; ks < Wq; ks += 16) {
+        unsigned a[4], b[4];
+        a[0] = *reinterpret_cast<const unsigned*>(qa + ks);
+        a[1] = *reinterpret_cast<const unsigned*>(qa + ks + 8 * P);
+        a[2] = *reinterpret_cast<const unsigned*>(qa + ks + 8);
+        a[3] = *reinterpret_cast<const unsigned*>(qa + ks + 8 * P + 8);
+        b[0] = *reinterpret_cast<const unsigned*>(ql + ks);
+        b[1] = *reinterpret_cast<const unsigned*>(ql + ks + 8 * P);
+        b[2] = *reinterpret_cast<const unsigned*>(ql + ks + 8);
+        b[3] = *reinterpret_cast<const unsigned*>(ql + ks + 8 * P + 8);
+        const unsigned k0 = *reinterpret_cast<const unsigned*>(kb + ks), k1 = *reinterpret_cast<const unsigned*>(kb + ks + 8);
+        lm_mma(c, a, k0, k1);
+        lm_mma(c, b, k0, k1);
+      }
+      const int kcol = warp * 8 + 2 * tq, key = tile * LM_KT + kcol;
+      const bool v0 = key >= key_lo && key <= pos, v1 = key + 1 >= key_lo && key + 1 <= pos;
+      Ss[g * 68 + kcol] = v0 ? c[0] * scale : -INFINITY;
+      Ss[g * 68 + kcol + 1] = v1 ? c[1] * scale : -INFINITY;
+      Ss[(g + 8) * 68 + kcol] = v0 ? c[2] * scale : -INFINITY;
+      Ss[(g + 8) * 68 + kcol + 1] = v1 ? c[3] * scale : -INFINITY;
+    }
+    __syncthreads();
+    {   // softmax of row tid / 16 over its 64 scores, 4 a thread
+      const int row = tid >> 4, c0 = (tid & 15) * 4;
+      float sv[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) sv[j] = Ss[row * 68 + c0 + j];
+      float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float m_old = m_s[row], m_new = fmaxf(m_old, mx);
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float pj = sv[j] > -INFINITY ? expf(sv[j] - m_new) : 0.f;
+        sum += pj;
+        bf16 hi = __float2bfloat16_rn(pj);
+        Ph[row * 72 + c0 + j] = hi;
+        Pl[row * 72 + c0 + j] = __float2bfloat16_rn(pj - __bfloat162float(hi));
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      __syncwarp();
+      if ((tid & 15) == 0) {
+        float corr = m_old > -INFINITY ? expf(m_old - m_new) : 0.f;
+        corr_s[row] = corr;
+        l_s[row] = l_s[row] * corr + sum;
+        m_s[row] = m_new;
+      }
+    }
+    __syncthreads();
+    {   // O += P V
+      const float cg = corr_s[g], cg8 = corr_s[g + 8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) { acc[i][0] *= cg; acc[i][1] *= cg; acc[i][2] *= cg8; acc[i][3] *= cg8; }
+#pragma unroll
+      for (int kk = 0; kk < LM_KT; kk += 16) {
+        unsigned ah[4], al[4];
+        const bf16* ph = Ph + g * 72 + kk + 2 * tq;
+        const bf16* pl = Pl + g * 72 + kk + 2 * tq;
+        ah[0] = *reinterpret_cast<const unsigned*>(ph);          al[0] = *reinterpret_cast<const unsigned*>(pl);
+        ah[1] = *reinterpret_cast<const unsigned*>(ph + 8 * 72); al[1] = *reinterpret_cast<const unsigned*>(pl + 8 * 72);
+        ah[2] = *reinterpret_cast<const unsigned*>(ph + 8);      al[2] = *reinterpret_cast<const unsigned*>(pl + 8);
+        ah[3] = *reinterpret_cast<const unsigned*>(ph + 8 * 72 + 8); al[3] = *reinterpret_cast<const unsigned*>(pl + 8 * 72 + 8);
+        const bf16* vrow = Kb + (size_t)(kk + (lane & 15)) * P;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const int j = warp + 8 * i;
+          if (j < n_ntiles) {
+            unsigned b0, b1;
+            unsigned addr = (unsigned)__cvta_generic_to_shared(vrow + j * 8);
+            asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(addr));
+            lm_mma(acc[i], ah, b0, b1);
+            lm_mma(acc[i], al, b0, b1);
+          }
+        }
+      }
+    }
+    __syncthreads();                                             // the buffer may be filled again
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int j = warp + 8 * i;
+    if (j >= n_ntiles) continue;
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      const int row = g + (q >> 1) * 8, h = h0 + row, col = j * 8 + 2 * tq + (q & 1);
+      if (h >= H) continue;
+      if (splits == 1) o_lat[((size_t)t * H + h) * r + col] = acc[i][q] / l_s[row];
+      else part_o[(((size_t)t * H + h) * splits + split) * r + col] = acc[i][q];
+    }
+  }
+  if (splits > 1 && tid < 16 && h0 + tid < H) {
+    size_t item = ((size_t)t * H + h0 + tid) * splits + split;
+    part_ml[2 * item] = m_s[tid];
+    part_ml[2 * item + 1] = l_s[tid];
+  }
+}
+
 // o_lat[t, h] = sum_s exp(m_s - M) o_s / sum_s exp(m_s - M) l_s; a split without keys has m = -inf and l = 0.
 __global__ void latent_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,
                                       int r, float* __restrict__ o_lat) {
@@ -276,6 +470,16 @@ latent_expand_kernel(const float* __restrict__ o_lat, const TW* __restrict__ wuv
 }
 
 // ----------------------------------------------------------------------------- launchers
+// QD_LATENT_MMA=0 in the environment keeps the float32-FMA attend kernel in bfloat16 too (to compare the two).
+static inline bool lm_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("QD_LATENT_MMA");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 extern "C" int qd_latent_prep(const float* u, long long ldu, int q_off, int q_rank, int kv_off, int r, int dr,
                               const float* wq_norm, const float* wkv_norm, float eps, const float* cos_t,
                               const float* sin_t, int rot_dims, const int* positions, const int* slot_map, void* cq,
@@ -319,6 +523,24 @@ extern "C" int qd_latent_attend(const float* qcat, const void* cache, int dtype,
   if (r > LA_MAX_R || r <= 0 || splits < 1 || splits > 65535 || H > 65535 * LA_WARPS || page_size <= 0) return QD_ERR_UNSUPPORTED;
   if (splits > 1 && (!part_o || !part_ml)) return QD_ERR_UNSUPPORTED;
   const int W = r + dr;
+  if (dtype == QD_BF16 && lm_enabled() && W % 8 == 0 && r % 8 == 0 && !((uintptr_t)cache & 15)) {
+    const int P = ((W + 15) & ~15) + 8;
+    size_t sm = (size_t)(32 + 2 * LM_KT) * P * 2 + 16 * 68 * 4 + 2 * 16 * 72 * 2 + 48 * 4;
+    if (sm <= 220 * 1024 && H <= 65535 * 16) {
+      static bool attr_set = false;
+      if (!attr_set) {
+        cudaFuncSetAttribute(latent_attend_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        attr_set = true;
+      }
+      qd_launch(latent_attend_mma_kernel, dim3(T, (H + 15) / 16, splits), dim3(256), sm, stream, qcat, (const bf16*)cache,
+                block_table, max_blocks, token_req, positions, H, r, dr, page_size, scale, window, splits, o_lat, part_o,
+                part_ml);
+      if (splits > 1)
+        qd_launch(latent_combine_kernel, dim3((unsigned)((size_t)T * H)), dim3(128), 0, stream, (const float*)part_o,
+                  (const float*)part_ml, splits, r, o_lat);
+      return qd_last_error();
+    }
+  }
   size_t smem = ((size_t)LA_TILE * (W + 1) + (size_t)LA_WARPS * W) * sizeof(float);
   if (smem > 200 * 1024) return QD_ERR_UNSUPPORTED;
   dim3 grid(T, (H + LA_WARPS - 1) / LA_WARPS, splits);
