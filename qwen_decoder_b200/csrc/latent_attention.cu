@@ -16,6 +16,22 @@
 // weights are the engine's dtype.  One template serves float32 and bfloat16.
 #include "common.cuh"
 
+// 16 bytes of a row as floats (8 bfloat16 or 4 float32)
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  __device__ static void load(const float* p, float* o) { float4 v = *reinterpret_cast<const float4*>(p); o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; }
+};
+template <> struct Vec16<bf16> {
+  static constexpr int N = 8;
+  __device__ static void load(const bf16* p, float* o) {
+    uint4 v = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) { o[2 * i] = __low2float(h[i]); o[2 * i + 1] = __high2float(h[i]); }
+  }
+};
+
 #define LA_WARPS 8
 #define LA_TILE 32          // keys per staged tile
 #define LA_MAX_R 512        // latent size the attend kernel takes (16 accumulators a lane)
@@ -65,7 +81,7 @@ template <typename TW>
 __global__ void __launch_bounds__(256)
 latent_absorb_kernel(const float* __restrict__ q, const TW* __restrict__ wuk, float* __restrict__ qcat, int T, int H,
                      int dn, int dr, int r, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                     int rot_dims, const int* __restrict__ positions) {
+                     int rot_dims, const int* __restrict__ positions, const float* __restrict__ pre) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float qs[];                // [LA_TT][dn]
@@ -78,6 +94,11 @@ latent_absorb_kernel(const float* __restrict__ q, const TW* __restrict__ wuk, fl
   }
   __syncthreads();
   for (int j = blockIdx.z * blockDim.x + threadIdx.x; j < r; j += gridDim.z * blockDim.x) {
+    if (pre) {          // the products were made elsewhere ([H, T, r]): only their place changes
+      for (int tt = 0; tt < nt; tt++)
+        qcat[((size_t)(t0 + tt) * H + h) * W + j] = pre[((size_t)h * T + t0 + tt) * r + j];
+      continue;
+    }
     float acc[LA_TT];
 #pragma unroll
     for (int tt = 0; tt < LA_TT; tt++) acc[tt] = 0.f;
@@ -102,6 +123,78 @@ latent_absorb_kernel(const float* __restrict__ q, const TW* __restrict__ wuk, fl
       float c = cos_t[(size_t)pos * half + pr], s = sin_t[(size_t)pos * half + pr];
       float a = qr[2 * pr], b = qr[2 * pr + 1];
       v = (e & 1) ? b * c + a * s : a * c - b * s;
+    } else {
+      v = qr[e];
+    }
+    qcat[((size_t)(t0 + tt) * H + h) * W + r + e] = v;
+  }
+}
+
+// The same with 16-byte loads of Wuk, for latent sizes whose pieces divide the CTA evenly (r / V a divisor of 256):
+// thread (jg, dg) owns V consecutive latent columns and every (256 * V / r)-th unrotated dimension; the groups'
+// partial sums meet in shared memory.  grid (token tiles, heads).
+template <typename TW>
+__global__ void __launch_bounds__(256)
+latent_absorb_vec_kernel(const float* __restrict__ q, const TW* __restrict__ wuk, float* __restrict__ qcat, int T, int H,
+                         int dn, int dr, int r, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                         int rot_dims, const int* __restrict__ positions) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int V = Vec16<TW>::N;
+  extern __shared__ float sm[];
+  float* qs = sm;                              // [LA_TT][dn]
+  float* red = sm + LA_TT * dn;                // [LA_TT][r]
+  const int h = blockIdx.y, t0 = blockIdx.x * LA_TT;
+  const int nt = min(LA_TT, T - t0);
+  const int W = r + dr, qw = H * (dn + dr);
+  for (int i = threadIdx.x; i < LA_TT * dn; i += blockDim.x) {
+    int tt = i / dn, d = i - tt * dn;
+    qs[i] = tt < nt ? q[(size_t)(t0 + tt) * qw + (size_t)h * (dn + dr) + d] : 0.f;
+  }
+  for (int i = threadIdx.x; i < LA_TT * r; i += blockDim.x) red[i] = 0.f;
+  __syncthreads();
+  const int JG = r / V, DG = 256 / JG;
+  const int jg = threadIdx.x % JG, dg = threadIdx.x / JG;
+  float acc[LA_TT][V];
+#pragma unroll
+  for (int tt = 0; tt < LA_TT; tt++)
+#pragma unroll
+    for (int v = 0; v < V; v++) acc[tt][v] = 0.f;
+  const TW* wbase = wuk + (size_t)h * dn * r + jg * V;
+#pragma unroll 4
+  for (int d = dg; d < dn; d += DG) {
+    float w[V];
+    Vec16<TW>::load(wbase + (size_t)d * r, w);
+#pragma unroll
+    for (int tt = 0; tt < LA_TT; tt++) {
+      const float qv = qs[tt * dn + d];
+#pragma unroll
+      for (int v = 0; v < V; v++) acc[tt][v] = fmaf(qv, w[v], acc[tt][v]);
+    }
+  }
+  for (int turn = 0; turn < DG; turn++) {        // the groups add in turn: the order of additions is fixed
+    if (dg == turn) {
+#pragma unroll
+      for (int tt = 0; tt < LA_TT; tt++)
+#pragma unroll
+        for (int v = 0; v < V; v++) red[tt * r + jg * V + v] += acc[tt][v];
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < nt * r; i += blockDim.x) {
+    int tt = i / r, j = i - tt * r;
+    qcat[((size_t)(t0 + tt) * H + h) * W + j] = red[i];
+  }
+  const int half = rot_dims >> 1;
+  for (int i = threadIdx.x; i < nt * dr; i += blockDim.x) {
+    int tt = i / dr, e = i - tt * dr;
+    const float* qr = q + (size_t)(t0 + tt) * qw + (size_t)h * (dn + dr) + dn;
+    float v;
+    if (e < rot_dims) {
+      int pr = e >> 1, pos = positions[t0 + tt];
+      float c = cos_t[(size_t)pos * half + pr], sn = sin_t[(size_t)pos * half + pr];
+      float a = qr[2 * pr], b = qr[2 * pr + 1];
+      v = (e & 1) ? b * c + a * sn : a * c - b * sn;
     } else {
       v = qr[e];
     }
@@ -429,28 +522,51 @@ __global__ void latent_combine_kernel(const float* __restrict__ part_o, const fl
 template <typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 latent_expand_kernel(const float* __restrict__ o_lat, const TW* __restrict__ wuv, const float* __restrict__ gate,
-                     long long ldg, TO* __restrict__ out, int T, int H, int dv, int r) {
+                     long long ldg, TO* __restrict__ out, int T, int H, int dv, int r, int vec,
+                     const float* __restrict__ pre) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float os[];                // [LA_TT][r]
   const int h = blockIdx.y, t0 = blockIdx.x * LA_TT;
   const int nt = min(LA_TT, T - t0);
+  const int i_hi = min(dv, (int)(blockIdx.z + 1) * 32);
+  if (pre) {            // Wuv_h o_lat was made elsewhere ([H, T, dv]): the gate and the rounding are left
+    for (int k = threadIdx.x; k < nt * 32; k += blockDim.x) {
+      int tt = k >> 5, i = blockIdx.z * 32 + (k & 31);
+      if (i >= i_hi) continue;
+      float v = pre[((size_t)h * T + t0 + tt) * dv + i];
+      if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)(t0 + tt) * ldg + (size_t)h * dv + i]));
+      out[(size_t)(t0 + tt) * H * dv + (size_t)h * dv + i] = from_float<TO>(v);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < LA_TT * r; i += blockDim.x) {
     int tt = i / r, j = i - tt * r;
     os[i] = tt < nt ? o_lat[((size_t)(t0 + tt) * H + h) * r + j] : 0.f;
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const int i_hi = min(dv, (int)(blockIdx.z + 1) * 32);
   for (int i = blockIdx.z * 32 + warp; i < i_hi; i += nw) {
     const TW* wrow = wuv + ((size_t)h * dv + i) * r;
     float acc[LA_TT];
 #pragma unroll
     for (int tt = 0; tt < LA_TT; tt++) acc[tt] = 0.f;
-    for (int j = lane; j < r; j += 32) {
-      float w = to_float(wrow[j]);
+    if (vec) {
+      constexpr int V = Vec16<TW>::N;
+      for (int j = lane * V; j < r; j += 32 * V) {
+        float w[V];
+        Vec16<TW>::load(wrow + j, w);
 #pragma unroll
-      for (int tt = 0; tt < LA_TT; tt++) acc[tt] = fmaf(w, os[tt * r + j], acc[tt]);
+        for (int tt = 0; tt < LA_TT; tt++)
+#pragma unroll
+          for (int v = 0; v < V; v++) acc[tt] = fmaf(w[v], os[tt * r + j + v], acc[tt]);
+      }
+    } else {
+      for (int j = lane; j < r; j += 32) {
+        float w = to_float(wrow[j]);
+#pragma unroll
+        for (int tt = 0; tt < LA_TT; tt++) acc[tt] = fmaf(w, os[tt * r + j], acc[tt]);
+      }
     }
 #pragma unroll
     for (int tt = 0; tt < LA_TT; tt++) acc[tt] = warp_sum(acc[tt]);
@@ -497,19 +613,36 @@ extern "C" int qd_latent_prep(const float* u, long long ldu, int q_off, int q_ra
   return qd_last_error();
 }
 
+// ``pre`` (float32 [H, T, r], or null): Wuk_h^T q_h already made by a batched library product; the kernel then only
+// lays it beside the rotated part.
 extern "C" int qd_latent_absorb(const float* q, const void* wuk, int w_dtype, float* qcat, int T, int H, int dn, int dr,
                                 int r, const float* cos_t, const float* sin_t, int rot_dims, const int* positions,
-                                cudaStream_t stream) {
+                                const float* pre, cudaStream_t stream) {
   if (T <= 0) return 0;
   size_t smem = (size_t)LA_TT * dn * sizeof(float);
   if (smem > 48 * 1024 || H > 65535) return QD_ERR_UNSUPPORTED;
+  {
+    const int V = w_dtype == QD_F32 ? 4 : 8;
+    const size_t vsm = (size_t)LA_TT * (dn + r) * sizeof(float);
+    if (!pre && (w_dtype == QD_F32 || w_dtype == QD_BF16) && r % V == 0 && r / V <= 256 && 256 % (r / V) == 0 &&
+        !((uintptr_t)wuk & 15) && vsm <= 48 * 1024) {
+      dim3 vgrid((T + LA_TT - 1) / LA_TT, H);
+      if (w_dtype == QD_F32)
+        qd_launch(latent_absorb_vec_kernel<float>, vgrid, dim3(256), vsm, stream, q, (const float*)wuk, qcat, T, H, dn, dr,
+                  r, cos_t, sin_t, rot_dims, positions);
+      else
+        qd_launch(latent_absorb_vec_kernel<bf16>, vgrid, dim3(256), vsm, stream, q, (const bf16*)wuk, qcat, T, H, dn, dr,
+                  r, cos_t, sin_t, rot_dims, positions);
+      return qd_last_error();
+    }
+  }
   dim3 grid((T + LA_TT - 1) / LA_TT, H, (r + 255) / 256);
   if (w_dtype == QD_F32)
     qd_launch(latent_absorb_kernel<float>, grid, dim3(256), smem, stream, q, (const float*)wuk, qcat, T, H, dn, dr, r,
-              cos_t, sin_t, rot_dims, positions);
+              cos_t, sin_t, rot_dims, positions, pre);
   else if (w_dtype == QD_BF16)
     qd_launch(latent_absorb_kernel<bf16>, grid, dim3(256), smem, stream, q, (const bf16*)wuk, qcat, T, H, dn, dr, r,
-              cos_t, sin_t, rot_dims, positions);
+              cos_t, sin_t, rot_dims, positions, pre);
   else
     return QD_ERR_UNSUPPORTED;
   return qd_last_error();
@@ -562,17 +695,19 @@ extern "C" int qd_latent_attend(const float* qcat, const void* cache, int dtype,
 }
 
 extern "C" int qd_latent_expand(const float* o_lat, const void* wuv, int w_dtype, const float* gate, long long ldg,
-                                void* out, int out_dtype, int T, int H, int dv, int r, cudaStream_t stream) {
+                                void* out, int out_dtype, int T, int H, int dv, int r, const float* pre,
+                                cudaStream_t stream) {
   if (T <= 0) return 0;
   size_t smem = (size_t)LA_TT * r * sizeof(float);
   if (smem > 48 * 1024 || H > 65535) return QD_ERR_UNSUPPORTED;
   dim3 grid((T + LA_TT - 1) / LA_TT, H, (dv + 31) / 32);
+  const int vec = (r % (w_dtype == QD_F32 ? 4 : 8) == 0 && !((uintptr_t)wuv & 15)) ? 1 : 0;     // rows in 16-byte pieces
   if (w_dtype == QD_F32 && out_dtype == QD_F32)
     qd_launch(latent_expand_kernel<float, float>, grid, dim3(256), smem, stream, o_lat, (const float*)wuv, gate, ldg,
-              (float*)out, T, H, dv, r);
+              (float*)out, T, H, dv, r, vec, pre);
   else if (w_dtype == QD_BF16 && out_dtype == QD_BF16)
     qd_launch(latent_expand_kernel<bf16, bf16>, grid, dim3(256), smem, stream, o_lat, (const bf16*)wuv, gate, ldg,
-              (bf16*)out, T, H, dv, r);
+              (bf16*)out, T, H, dv, r, vec, pre);
   else
     return QD_ERR_UNSUPPORTED;
   return qd_last_error();

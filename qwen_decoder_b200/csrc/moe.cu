@@ -249,36 +249,46 @@ moe_gemv_kernel(const TI* __restrict__ A, long long lda, const int* __restrict__
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int V = Vec16<TW>::N;                // TI and TW are the same type in every instantiation
-  for (int i = 0; i < 8; i++) {
+  // two output rows at a time: twice the loads in flight for the same registers of x
+  for (int i = 0; i < 8; i += 2) {
     const int n = blockIdx.x * 64 + warp * 8 + i;
     if (n >= N) break;
-    const TW* w1 = W1 + ((size_t)e * N + n) * K;
-    const TW* w2 = GATED ? W2 + ((size_t)e * N + n) * K : nullptr;
-    float a1[MG_ROWS], a2[MG_ROWS];
+    const bool two = n + 1 < N;
+    const TW* w1a = W1 + ((size_t)e * N + n) * K;
+    const TW* w1b = two ? w1a + K : w1a;
+    const TW* w2a = GATED ? W2 + ((size_t)e * N + n) * K : nullptr;
+    const TW* w2b = GATED ? (two ? w2a + K : w2a) : nullptr;
+    float a1[2][MG_ROWS], a2[2][MG_ROWS];
 #pragma unroll
-    for (int r = 0; r < MG_ROWS; r++) a1[r] = a2[r] = 0.f;
+    for (int r = 0; r < MG_ROWS; r++) a1[0][r] = a1[1][r] = a2[0][r] = a2[1][r] = 0.f;
     for (int k = lane * V; k < K; k += 32 * V) {
-      float w1v[V], w2v[V], xv[V];
-      Vec16<TW>::load(w1 + k, w1v);
-      if (GATED) Vec16<TW>::load(w2 + k, w2v);
+      float wa[V], wb[V], ga[V], gb[V], xv[V];
+      Vec16<TW>::load(w1a + k, wa);
+      Vec16<TW>::load(w1b + k, wb);
+      if (GATED) { Vec16<TW>::load(w2a + k, ga); Vec16<TW>::load(w2b + k, gb); }
 #pragma unroll
       for (int r = 0; r < MG_ROWS; r++) {
         if (r < rows) {
           Vec16<TI>::load(xs + (size_t)r * K + k, xv);
 #pragma unroll
           for (int j = 0; j < V; j++) {
-            a1[r] = fmaf(xv[j], w1v[j], a1[r]);
-            if (GATED) a2[r] = fmaf(xv[j], w2v[j], a2[r]);
+            a1[0][r] = fmaf(xv[j], wa[j], a1[0][r]);
+            a1[1][r] = fmaf(xv[j], wb[j], a1[1][r]);
+            if (GATED) { a2[0][r] = fmaf(xv[j], ga[j], a2[0][r]); a2[1][r] = fmaf(xv[j], gb[j], a2[1][r]); }
           }
         }
       }
     }
 #pragma unroll
-    for (int r = 0; r < MG_ROWS; r++) {
-      if (r < rows) {
-        float v = warp_sum(a1[r]);
-        if (GATED) v = v / (1.0f + expf(-v)) * warp_sum(a2[r]);
-        if (lane == 0) out[(size_t)(row0 + r) * N + n] = from_float<TO>(v);
+    for (int u = 0; u < 2; u++) {
+      if (u == 1 && !two) break;
+#pragma unroll
+      for (int r = 0; r < MG_ROWS; r++) {
+        if (r < rows) {
+          float v = warp_sum(a1[u][r]);
+          if (GATED) v = v / (1.0f + expf(-v)) * warp_sum(a2[u][r]);
+          if (lane == 0) out[(size_t)(row0 + r) * N + n + u] = from_float<TO>(v);
+        }
       }
     }
   }

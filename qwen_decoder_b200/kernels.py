@@ -721,16 +721,19 @@ def latent_prep(u: torch.Tensor, q_off: int, q_rank: int, kv_off: int, r: int, d
 
 
 def latent_absorb(q: torch.Tensor, wuk: torch.Tensor, qcat: torch.Tensor, H: int, dn: int, dr: int, r: int,
-                  cos: torch.Tensor, sin: torch.Tensor, rot_dims: int, positions: torch.Tensor) -> None:
+                  cos: torch.Tensor, sin: torch.Tensor, rot_dims: int, positions: torch.Tensor,
+                  pre: Optional[torch.Tensor] = None) -> None:
     """qcat[t, h] = [Wuk_h^T q_unrotated[t, h] (r) | rotate(q_rotated[t, h]) (dr)], float32; q float32
-    [T, H * (dn + dr)], wuk [H * dn, r]."""
+    [T, H * (dn + dr)], wuk [H * dn, r].  ``pre`` (float32 [H, T, r]): the first part, already made by a batched
+    library product."""
+    assert pre is None or (pre.dtype == torch.float32 and pre.shape == (H, q.shape[0], r) and pre.is_contiguous())
     T = q.shape[0]
     assert q.dtype == torch.float32 and q.shape == (T, H * (dn + dr)) and wuk.shape == (H * dn, r)
     assert qcat.dtype == torch.float32 and qcat.shape == (T, H, r + dr)
     _contig(q, "q"); _contig(wuk, "wuk"); _contig(qcat, "qcat")
     _check(library("latent_attention").qd_latent_absorb(
         _ptr(q), _ptr(wuk), _I(dtype_code(wuk.dtype)), _ptr(qcat), _I(T), _I(H), _I(dn), _I(dr), _I(r), _ptr(cos),
-        _ptr(sin), _I(rot_dims), _ptr(positions), _stream()), "latent_absorb")
+        _ptr(sin), _I(rot_dims), _ptr(positions), _ptr(pre), _stream()), "latent_absorb")
 
 
 def latent_attend(qcat: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, token_req: torch.Tensor,
@@ -756,16 +759,18 @@ def latent_attend(qcat: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
 
 
 def latent_expand(o_lat: torch.Tensor, wuv: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor,
-                  dv: int) -> None:
+                  dv: int, pre: Optional[torch.Tensor] = None) -> None:
     """out[t, h * dv + i] = (Wuv_h o_lat[t, h])[i] * sigmoid(gate[t, h * dv + i]); gate float32 (a column slice of a
     wider buffer is fine) or None."""
     T, H, r = o_lat.shape
     assert wuv.shape == (H * dv, r) and out.shape == (T, H * dv) and out.dtype == wuv.dtype
     assert gate is None or (gate.dtype == torch.float32 and gate.shape == (T, H * dv) and gate.stride(1) == 1)
+    # ``pre`` (float32 [H, T, dv]): Wuv_h o_lat[t, h] already made by a batched library product
+    assert pre is None or (pre.dtype == torch.float32 and pre.shape == (H, T, dv) and pre.is_contiguous())
     _contig(o_lat, "o_lat"); _contig(wuv, "wuv"); _contig(out, "out")
     _check(library("latent_attention").qd_latent_expand(
         _ptr(o_lat), _ptr(wuv), _I(dtype_code(wuv.dtype)), _ptr(gate), _LL(gate.stride(0) if gate is not None else 0),
-        _ptr(out), _I(dtype_code(out.dtype)), _I(T), _I(H), _I(dv), _I(r), _stream()), "latent_expand")
+        _ptr(out), _I(dtype_code(out.dtype)), _I(T), _I(H), _I(dv), _I(r), _ptr(pre), _stream()), "latent_expand")
 
 
 # ------------------------------------------------------------------ state-space mixer

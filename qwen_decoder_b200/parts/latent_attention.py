@@ -25,7 +25,20 @@ from ..cache import PagedRows
 from ..config.registry import register_part
 from ..weights.loader import TensorSource, TensorSpec
 from .base import Mixer, PagedCacheView
+from . import matmul_backend
 from .linear import Linear
+
+# From this many tokens on, the bfloat16 engine makes the per-head products with Wuk and Wuv as batched library
+# products (as the framework does for every product of many tokens); below, the kernels read the weights themselves.
+LIBRARY_TOKENS = 64
+
+
+def _hi_lo(x: torch.Tensor) -> torch.Tensor:
+    """float32 [T, H, d] -> bfloat16 [H, T, 2 d]: every number as its bfloat16 rounding and what that left out,
+    side by side, so that a bfloat16 product with a matrix stacked twice sees 16 bits of mantissa."""
+    hi = x.to(torch.bfloat16)
+    lo = (x - hi.float()).to(torch.bfloat16)
+    return torch.cat((hi, lo), dim=-1).transpose(0, 1)
 
 
 def attend_splits(ctas_without_split: int, max_keys: int) -> int:
@@ -75,6 +88,13 @@ class LatentAttention(Mixer):
         self.w_dq_norm, self.w_dkv_norm = f32(f"{p}dq.norm"), f32(f"{p}dkv.norm")
         self.w_uk = source.get(f"{p}uk{s}").to(device=device, dtype=dtype).contiguous()
         self.w_uv = source.get(f"{p}uv{s}").to(device=device, dtype=dtype).contiguous()
+        H = self.num_heads
+        # for the batched library products: each matrix twice along its inner dimension, so that a float32 operand
+        # can enter as [hi | lo] (two bfloat16 numbers per element) in ONE product with a float32 sum
+        uk = self.w_uk.view(H, self.nope_dim, self.kv_rank)                                  # [H, dn, r]
+        uv = self.w_uv.view(H, self.v_dim, self.kv_rank).transpose(1, 2)                     # [H, r, dv]
+        self.w_uk_twice = torch.cat((uk, uk), dim=1).contiguous() if dtype == torch.bfloat16 else None
+        self.w_uv_twice = torch.cat((uv, uv), dim=1).contiguous() if dtype == torch.bfloat16 else None
         self._no_table = torch.zeros((1, 0), dtype=torch.float32, device=device)
 
     def forward(self, x: torch.Tensor, ctx, cache: PagedCacheView) -> torch.Tensor:
@@ -88,7 +108,13 @@ class LatentAttention(Mixer):
                             cache.group.slot_map, cq, cache.kv, cache.write)
         q = self.up_q.forward(cq, out_dtype=torch.float32)
         qcat = torch.empty((T, H, r + dr), dtype=torch.float32, device=x.device)
-        kernels.latent_absorb(q, self.w_uk, qcat, H, dn, dr, r, *rot, ctx.positions)
+        library = x.dtype == torch.bfloat16 and T >= LIBRARY_TOKENS and matmul_backend.mode != "generic"
+        pre = None
+        if library:
+            qn = _hi_lo(q.view(T, H, dn + dr)[:, :, :dn])                                   # [H, T, 2 dn]
+            pre = torch.bmm(qn, self.w_uk_twice, out_dtype=torch.float32)                   # [H, T, r]
+            matmul_backend.counters["library"] += 1
+        kernels.latent_absorb(q, self.w_uk, qcat, H, dn, dr, r, *rot, ctx.positions, pre=pre)
         o_lat = torch.empty((T, H, r), dtype=torch.float32, device=x.device)
         window = self.window or 0
         groups = -(-H // 8)
@@ -96,5 +122,9 @@ class LatentAttention(Mixer):
         kernels.latent_attend(qcat, cache.kv, cache.group.block_table, ctx.token_request, ctx.positions, r, dr,
                               cache.group.page_size, self.scale, window, splits, o_lat)
         attn = torch.empty((T, H * dv), dtype=x.dtype, device=x.device)
-        kernels.latent_expand(o_lat, self.w_uv, u[:, qr + r + dr:], attn, dv)
+        pre = None
+        if library:
+            pre = torch.bmm(_hi_lo(o_lat), self.w_uv_twice, out_dtype=torch.float32)        # [H, T, dv]
+            matmul_backend.counters["library"] += 1
+        kernels.latent_expand(o_lat, self.w_uv, u[:, qr + r + dr:], attn, dv, pre=pre)
         return self.out.forward_partial(attn)
