@@ -366,9 +366,52 @@ def _model_tensors(model):
     return out
 
 
+def latent_attend_micro(args):
+    """``--micro latent_attend``: the latent-attention kernel alone, ``--batch`` decoding tokens (one per request) at
+    ``--context`` cached rows each, heads and sizes of ``--hybrid-size``; bytes = the cached rows read once."""
+    import torch
+    from qwen_decoder_b200 import kernels
+    from qwen_decoder_b200.parts.latent_attention import attend_splits
+    z = HYBRID_SIZES[args.hybrid_size]["latent"]
+    H, r, dr = z["heads"], z["kv_rank"], z["rot_dim"]
+    B, ctx, ps = args.batch, args.context, args.page_size
+    dev = torch.device("cuda:0")
+    pages_per = (ctx + ps - 1) // ps
+    cache = torch.randn((B * pages_per + 1, ps, r + dr), device=dev).to(torch.bfloat16)
+    bt = torch.randperm(B * pages_per, device=dev).to(torch.int32).view(B, pages_per).contiguous()
+    qcat = torch.randn((B, H, r + dr), device=dev)
+    o_lat = torch.empty((B, H, r), device=dev)
+    token_req = torch.arange(B, dtype=torch.int32, device=dev)
+    positions = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+    splits = attend_splits(B * (-(-H // 16)), ctx)
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)       # 256 MB: larger than L2
+    run = lambda: kernels.latent_attend(qcat, cache, bt, token_req, positions, r, dr, ps, (r + dr) ** -0.5, 0, splits, o_lat)
+    for _ in range(3):
+        run()
+    times = []
+    for _ in range(max(3, min(args.steps, 20))):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    us = sorted(times)[len(times) // 2]
+    nbytes = B * ctx * (r + dr) * 2
+    pk, src = peaks()
+    print(json.dumps({"micro": "latent_attend", "batch": B, "context": ctx, "heads": H, "kv_rank": r, "rot_dim": dr,
+                      "splits": splits, "us": round(us, 2), "gb_per_s": round(nbytes / us / 1e3, 1),
+                      "frac_of_hbm": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3), "peaks": src,
+                      "l2": "256 MB written between timed launches"}))
+    return 0
+
+
 def micro(args):
     if args.micro == "hybrid":
         return hybrid_bench(args)
+    if args.micro == "latent_attend":
+        return latent_attend_micro(args)
     """One kernel alone: W-streaming contraction, decode attention or prefill attention at the 3B sizes."""
     if args.micro == "serve":
         return serve(args)
@@ -618,7 +661,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--timeline", action="store_true",
                     help="with --micro prefill_attention: print the kernel's own time stamps of one CTA (microseconds) to stderr")
-    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention", "serve", "mixed_step", "hybrid"],
+    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention", "serve", "mixed_step", "hybrid", "latent_attend"],
                     help="time one kernel alone at the 3B shape (for profiles/), or with 'serve' a whole run of "
                          "--batch requests (--context prompt tokens, --steps new tokens each) through the entry "
                          "point; print one JSON line and exit")

@@ -75,7 +75,7 @@ def _check_layer(i: int, layer: Mapping[str, Any]) -> None:
         top = _need(f.get("router"), "top", f"{where}.mlp.router")
         if top > e:
             raise ConfigError(f"config.json: {where}.mlp.router.top ({top}) exceeds experts ({e})")
-        if f.get("shared") is not None:
+        if f.get("shared"):                     # absent, null or empty: no shared expert
             _need(f["shared"], "ff", f"{where}.mlp.shared")
     else:
         raise ConfigError(f"config.json: {where}.mlp.kind must be 'dense' or 'moe', got {fk!r}")

@@ -345,14 +345,18 @@ latent_attend_mma_kernel(const float* __restrict__ qcat, const bf16* __restrict_
   const int my_hi = tile_lo + (int)((long long)n_tiles * (split + 1) / splits);
   const int pieces = W >> 3;                                     // 16-byte pieces of a cached row
 
+  // a warp copies whole rows (8 of the 64 each): the page lookup once per row, then 16-byte pieces lane by lane
   auto issue = [&](int tile, int buf) {
     bf16* dst = Ks + (size_t)buf * LM_KT * P;
-    for (int p = tid; p < LM_KT * pieces; p += 256) {
-      int row = p / pieces, c = p - row * pieces, key = tile * LM_KT + row;
-      bool ok = key >= key_lo && key <= pos;
-      const bf16* src = ok ? cache + ((size_t)bt[key / page_size] * page_size + key % page_size) * W + c * 8 : cache;
-      unsigned d = (unsigned)__cvta_generic_to_shared(dst + row * P + c * 8);
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(ok ? 16 : 0) : "memory");
+    for (int row = warp; row < LM_KT; row += 8) {
+      const int key = tile * LM_KT + row;
+      const bool ok = key >= key_lo && key <= pos;
+      const bf16* src = ok ? cache + ((size_t)bt[key / page_size] * page_size + key % page_size) * W : cache;
+      const unsigned d = (unsigned)__cvta_generic_to_shared(dst + row * P);
+      const unsigned n = ok ? 16u : 0u;
+      for (int c = lane; c < pieces; c += 32)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d + 16u * c), "l"(ok ? src + 8 * c : src), "r"(n)
+                     : "memory");
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
@@ -389,24 +393,33 @@ latent_attend_mma_kernel(const float* __restrict__ qcat, const bf16* __restrict_
     __syncthreads();
     const bf16* Kb = Ks + (size_t)buf * LM_KT * P;
     {   // S = Q K^T for this warp's 8 keys
-      float c[4] = {0.f, 0.f, 0.f, 0.f};
-      const bf16* qa = Qs + g * P + 2 * tq;
-      const bf16* ql = Ql + g * P + 2 * tq;
-      const bf16* kb = Kb + (warp * 8 + g) * P + 2 * tq;
-      for (int ks = 0; ks < Wq; ks += 16) {
-        unsigned a[4], b[4];
-        a[0] = *reinterpret_cast<const unsigned*>(qa + ks);
-        a[1] = *reinterpret_cast<const unsigned*>(qa + ks + 8 * P);
-        a[2] = *reinterpret_cast<const unsigned*>(qa + ks + 8);
-        a[3] = *reinterpret_cast<const unsigned*>(qa + ks + 8 * P + 8);
-        b[0] = *reinterpret_cast<const unsigned*>(ql + ks);
-        b[1] = *reinterpret_cast<const unsigned*>(ql + ks + 8 * P);
-        b[2] = *reinterpret_cast<const unsigned*>(ql + ks + 8);
-        b[3] = *reinterpret_cast<const unsigned*>(ql + ks + 8 * P + 8);
-        const unsigned k0 = *reinterpret_cast<const unsigned*>(kb + ks), k1 = *reinterpret_cast<const unsigned*>(kb + ks + 8);
-        lm_mma(c, a, k0, k1);
-        lm_mma(c, b, k0, k1);
+      // four independent sums (hi and lo, even and odd steps): one sum would chain every MMA to the one before
+      float c4[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) c4[u][0] = c4[u][1] = c4[u][2] = c4[u][3] = 0.f;
+      // operands by ldmatrix: the 16 x 16 piece of the queries (hi, lo) as four 8 x 8 matrices, the 8 keys x 16 as two
+      const unsigned q_hi = (unsigned)__cvta_generic_to_shared(Qs + (lane & 15) * P + (lane >> 4) * 8);
+      const unsigned q_lo = (unsigned)__cvta_generic_to_shared(Ql + (lane & 15) * P + (lane >> 4) * 8);
+      const unsigned k_ad = (unsigned)__cvta_generic_to_shared(Kb + (warp * 8 + (lane & 7)) * P + ((lane >> 3) & 1) * 8);
+      auto step = [&](int ks, float* ch, float* cl) {
+        unsigned a[4], b[4], k0, k1;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                     : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(q_hi + 2u * ks));
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                     : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(q_lo + 2u * ks));
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(k0), "=r"(k1) : "r"(k_ad + 2u * ks));
+        lm_mma(ch, a, k0, k1);
+        lm_mma(cl, b, k0, k1);
+      };
+      int ks = 0;
+      for (; ks + 32 <= Wq; ks += 32) {
+        step(ks, c4[0], c4[1]);
+        step(ks + 16, c4[2], c4[3]);
       }
+      if (ks < Wq) step(ks, c4[0], c4[1]);
+      float c[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) c[u] = (c4[0][u] + c4[2][u]) + (c4[1][u] + c4[3][u]);
       const int kcol = warp * 8 + 2 * tq, key = tile * LM_KT + kcol;
       const bool v0 = key >= key_lo && key <= pos, v1 = key + 1 >= key_lo && key + 1 <= pos;
       Ss[g * 68 + kcol] = v0 ? c[0] * scale : -INFINITY;
@@ -451,12 +464,12 @@ latent_attend_mma_kernel(const float* __restrict__ qcat, const bf16* __restrict_
 #pragma unroll
       for (int kk = 0; kk < LM_KT; kk += 16) {
         unsigned ah[4], al[4];
-        const bf16* ph = Ph + g * 72 + kk + 2 * tq;
-        const bf16* pl = Pl + g * 72 + kk + 2 * tq;
-        ah[0] = *reinterpret_cast<const unsigned*>(ph);          al[0] = *reinterpret_cast<const unsigned*>(pl);
-        ah[1] = *reinterpret_cast<const unsigned*>(ph + 8 * 72); al[1] = *reinterpret_cast<const unsigned*>(pl + 8 * 72);
-        ah[2] = *reinterpret_cast<const unsigned*>(ph + 8);      al[2] = *reinterpret_cast<const unsigned*>(pl + 8);
-        ah[3] = *reinterpret_cast<const unsigned*>(ph + 8 * 72 + 8); al[3] = *reinterpret_cast<const unsigned*>(pl + 8 * 72 + 8);
+        const unsigned p_hi = (unsigned)__cvta_generic_to_shared(Ph + (lane & 15) * 72 + kk + (lane >> 4) * 8);
+        const unsigned p_lo = (unsigned)__cvta_generic_to_shared(Pl + (lane & 15) * 72 + kk + (lane >> 4) * 8);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                     : "=r"(ah[0]), "=r"(ah[1]), "=r"(ah[2]), "=r"(ah[3]) : "r"(p_hi));
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                     : "=r"(al[0]), "=r"(al[1]), "=r"(al[2]), "=r"(al[3]) : "r"(p_lo));
         const bf16* vrow = Kb + (size_t)(kk + (lane & 15)) * P;
 #pragma unroll
         for (int i = 0; i < 8; i++) {
