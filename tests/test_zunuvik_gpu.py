@@ -57,6 +57,7 @@ ONE_LAYER = {
     "latent": (zc.latent(3, 16, 8, 24, 40, 32), None),
     "latent_part_rotated": (zc.latent(2, 8, 16, 8, 24, 40, rot_dims=6, base=37.0, scale=0.9), None),
     "latent_many_heads": (zc.latent(11, 8, 4, 8, 16, 24), None),
+    "latent_two_head_tiles": (zc.latent(20, 8, 8, 16, 24, 32), None),       # more heads than one 16-row tile holds
     "mamba": (zc.mamba(4, 12, 20, 2, 4, 2), None),
     "mamba_one_tap": (zc.mamba(3, 8, 300, 1, 1, 1), None),
     "mamba_wide_state": (zc.mamba(2, 40, 130, 2, 3, 5), None),
