@@ -26,13 +26,19 @@ from .prefix import PrefixIndex
 @dataclass(frozen=True)
 class PagedKV:
     """Keys and values of ``num_kv_heads`` x ``head_dim`` per token; ``window`` = None keeps
-    all of them, an integer keeps the last ``window`` positions readable."""
+    all of them, an integer keeps the last ``window`` positions readable.  ``v_dim``: the size of a
+    value where it differs from a key's; a page is then one flat row, the keys
+    [kv heads, offset in page, head_dim] followed by the values [kv heads, offset in page, v_dim]
+    (with equal sizes this is the same memory as [K|V, kv heads, offset in page, head_dim])."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_dim: Optional[int] = None
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
-        return (2, self.num_kv_heads, page_size, self.head_dim)
+        if self.v_dim is None or self.v_dim == self.head_dim:
+            return (2, self.num_kv_heads, page_size, self.head_dim)
+        return (self.num_kv_heads * page_size * (self.head_dim + self.v_dim),)
 
 
 @dataclass(frozen=True)

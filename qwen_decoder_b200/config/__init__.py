@@ -7,9 +7,10 @@ from .registry import (
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from . import qwen2 as _qwen2  # registers Qwen2ForCausalLM
 from .zunuvik import ZunuvikConfig  # registers Zunuvik
+from .veterax import VeteraxConfig  # registers Veterax
 
 __all__ = [
-    "ConfigError", "Qwen2Config", "ZunuvikConfig", "read_config_json", "write_config_json", "PART_KINDS",
+    "ConfigError", "Qwen2Config", "ZunuvikConfig", "VeteraxConfig", "read_config_json", "write_config_json", "PART_KINDS",
     "config_from_dict", "create_part", "describe_model", "known_architectures", "load_config",
     "lookup_architecture", "register_architecture", "register_part", "unregister_architecture",
     "unregister_part", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry",

@@ -45,6 +45,8 @@ LIBRARIES: Dict[str, str] = {
     "latent_attention": "latent_attention.cu",
     "mamba2": "mamba2.cu",
     "moe": "moe.cu",
+    "norm_act": "norm_act.cu",
+    "attention_sink": "attention_sink.cu",
 }
 HEADERS = ["common.cuh", "entry_points.h"]
 # further files a library's source includes (hashed into its key)

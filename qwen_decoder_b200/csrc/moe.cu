@@ -8,12 +8,27 @@
 //   down     y[place] = Wd_e act[place]                                    float32            } a tile = one expert
 //   combine  out[t] = sum_k weight[t, k] y[place(t, k)] + gate[t] * shared[t]                  float32
 //
+// Variants, all parameters of the launchers: the router may instead take the softmax over ALL its outputs, choose by
+// score + a per-output correction and weigh by the plain score (``route_mode`` 1); the last outputs of the router
+// may be identity experts, which have no weights and whose output is the token's input itself (they get no row
+// tiles; combine adds weight * input); the gated activation may be the clamped form
+// min(g, L) * sigmoid(a * min(g, L)) * (clamp(u, -L, L) + 1) (``act`` 1) instead of silu(g) * u.
+//
 // Nothing comes back to the host between these: counts, places and tiles stay on the device, so a step with
 // routed experts is captured in a CUDA graph like any other.  The products run on float32 FMA with the
 // weights in the engine's dtype; a tile's rows are pairs of one expert, its sums one FMA chain over k each.
 #include "common.cuh"
 
 #define MOE_MAX_TOP 32
+
+// The gate of a gated expert: act 0 silu(g) * u; act 1 the clamped form with slope ``alpha`` and limit ``limit``.
+struct MoeAct { int kind; float limit, alpha; };
+__device__ __forceinline__ float moe_gated(float g, float u, MoeAct a) {
+  if (a.kind == 0) return g / (1.0f + expf(-g)) * u;
+  g = fminf(g, a.limit);
+  u = fminf(fmaxf(u, -a.limit), a.limit);
+  return g / (1.0f + expf(-a.alpha * g)) * (u + 1.0f);
+}
 
 // ----------------------------------------------------------------------------- route
 // 16 bytes of a row as floats (8 bfloat16 or 4 float32)
@@ -77,22 +92,45 @@ moe_logits_kernel(const T* __restrict__ h, const T* __restrict__ wr, const float
   for (int i = 0; i < MR_TOKENS; i++) {
     float v = warp_sum(acc[i]);
     if (lane == 0 && i < nt) {
-      if (e < E) logits[(size_t)(t0 + i) * E + e] = v + br[e];
+      if (e < E) logits[(size_t)(t0 + i) * E + e] = v + (br ? br[e] : 0.0f);
       else sgate[t0 + i] = 1.0f / (1.0f + expf(-v));
     }
   }
 }
 
-// One thread per token: the ``top`` largest logits (the lower index wins a tie) and the softmax over them.
+// One thread per token.  mode 0: the ``top`` largest logits (the lower index wins a tie) and the softmax over them.
+// mode 1: scores = softmax over all E logits; the ``top`` largest of score + corr[e] are chosen (the lower index wins
+// a tie); the weights are the chosen outputs' plain scores, not renormalised.
 __global__ void __launch_bounds__(128)
-moe_topk_kernel(float* __restrict__ logits, int n_tokens, int E, int top, int* __restrict__ idx,
-                float* __restrict__ wt) {
+moe_topk_kernel(float* __restrict__ logits, int n_tokens, int E, int top, int mode, const float* __restrict__ corr,
+                int* __restrict__ idx, float* __restrict__ wt) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= n_tokens) return;
   float* my = logits + (size_t)t * E;
   float v[MOE_MAX_TOP];
+  if (mode == 1) {
+    float zmax = -INFINITY, sum = 0.f;
+    for (int e = 0; e < E; e++) zmax = fmaxf(zmax, my[e]);
+    for (int e = 0; e < E; e++) sum += expf(my[e] - zmax);
+    const float inv = 1.0f / sum;
+    for (int e = 0; e < E; e++) my[e] = expf(my[e] - zmax) * inv;        // the scores, in place
+    for (int k = 0; k < top; k++) {
+      int best = -1;
+      float bv = -INFINITY;
+      for (int e = 0; e < E; e++) {
+        float s = my[e];
+        if (s < 0.f) continue;                                           // taken already
+        float c = s + (corr ? corr[e] : 0.f);
+        if (best < 0 || c > bv) { best = e; bv = c; }
+      }
+      idx[(size_t)t * top + k] = best;
+      wt[(size_t)t * top + k] = my[best];
+      my[best] = -1.0f;
+    }
+    return;
+  }
   for (int k = 0; k < top; k++) {
     int best = -1;
     float bv = -INFINITY;
@@ -113,8 +151,8 @@ moe_topk_kernel(float* __restrict__ logits, int n_tokens, int E, int top, int* _
 // ----------------------------------------------------------------------------- sort
 // One CTA.  meta: [0, E] offsets (E + 1), then n_tiles, then tiles (expert, first row, rows) x max_tiles.
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* __restrict__ idx, int n_pairs, int E, int tile_rows, int max_tiles, int* __restrict__ place,
-                int* __restrict__ pair_at, int* __restrict__ meta) {
+moe_sort_kernel(const int* __restrict__ idx, int n_pairs, int E, int E_real, int tile_rows, int max_tiles,
+                int* __restrict__ place, int* __restrict__ pair_at, int* __restrict__ meta) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ int cnt[];                  // [E] counts, then [E] cursors
@@ -129,7 +167,7 @@ moe_sort_kernel(const int* __restrict__ idx, int n_pairs, int E, int tile_rows, 
     for (int e = 0; e < E; e++) {
       meta[e] = off;
       cur[e] = off;
-      for (int r0 = 0; r0 < cnt[e] && nt < max_tiles; r0 += tile_rows) {
+      for (int r0 = 0; e < E_real && r0 < cnt[e] && nt < max_tiles; r0 += tile_rows) {   // identity experts: no tiles
         tiles[3 * nt] = e;
         tiles[3 * nt + 1] = off + r0;
         tiles[3 * nt + 2] = min(tile_rows, cnt[e] - r0);
@@ -155,7 +193,7 @@ template <typename TI, typename TW, typename TO, int TM, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TI* __restrict__ A, long long lda, const int* __restrict__ pair_at, int top, int by_token,
                 const TW* __restrict__ W1, const TW* __restrict__ W2, TO* __restrict__ out, int N, int K,
-                const int* __restrict__ meta, int E) {
+                const int* __restrict__ meta, int E, MoeAct act) {
   pdl_launch_dependents();
   pdl_wait();
   const int n_tiles = meta[E + 1];
@@ -217,7 +255,7 @@ moe_gemm_kernel(const TI* __restrict__ A, long long lda, const int* __restrict__
       int gn = n0 + tx * 4 + j;
       if (gn >= N) continue;
       float v = acc1[i][j];
-      if (GATED) v = v / (1.0f + expf(-v)) * acc2[i][j];
+      if (GATED) v = moe_gated(v, acc2[i][j], act);
       out[(size_t)(row0 + r) * N + gn] = from_float<TO>(v);
     }
   }
@@ -232,7 +270,7 @@ template <typename TI, typename TW, typename TO, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_gemv_kernel(const TI* __restrict__ A, long long lda, const int* __restrict__ pair_at, int top, int by_token,
                 const TW* __restrict__ W1, const TW* __restrict__ W2, TO* __restrict__ out, int N, int K,
-                const int* __restrict__ meta, int E) {
+                const int* __restrict__ meta, int E, MoeAct act) {
   pdl_launch_dependents();
   pdl_wait();
   if ((int)blockIdx.y >= meta[E + 1]) return;
@@ -286,7 +324,7 @@ moe_gemv_kernel(const TI* __restrict__ A, long long lda, const int* __restrict__
       for (int r = 0; r < MG_ROWS; r++) {
         if (r < rows) {
           float v = warp_sum(a1[u][r]);
-          if (GATED) v = v / (1.0f + expf(-v)) * warp_sum(a2[u][r]);
+          if (GATED) v = moe_gated(v, warp_sum(a2[u][r]), act);
           if (lane == 0) out[(size_t)(row0 + r) * N + n + u] = from_float<TO>(v);
         }
       }
@@ -309,7 +347,7 @@ template <typename TO, bool GATED>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ pair_at, int top, int by_token,
                     const bf16* __restrict__ W1, const bf16* __restrict__ W2, TO* __restrict__ out, int N, int K,
-                    const int* __restrict__ meta, int E) {
+                    const int* __restrict__ meta, int E, MoeAct act) {
   pdl_launch_dependents();
   pdl_wait();
   if ((int)blockIdx.y >= meta[E + 1]) return;
@@ -386,7 +424,7 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
       int r = warp * 16 + g + (q >> 1) * 8, n = n0 + j * 8 + 2 * tq + (q & 1);
       if (r < rows && n < N) {
         float v = c1[j][q];
-        if (GATED) v = v / (1.0f + expf(-v)) * c2[j][q];
+        if (GATED) v = moe_gated(v, c2[j][q], act);
         out[(size_t)(row0 + r) * N + n] = from_float<TO>(v);
       }
     }
@@ -394,22 +432,27 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
 
 // ----------------------------------------------------------------------------- combine
 // out[t, :] = sum_k wt[t, k] * y[place[t * top + k], :] + sgate[t] * sum_p shared[p, t, :]   (float32 out)
-template <typename TS>
+// A pair whose expert index is E_real or more is an identity expert: its output is the token's input h[t, :].
+// sgate may be null: the shared expert then counts in full.
+template <typename TS, typename TH>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, const float* __restrict__ wt, int top,
                    const TS* __restrict__ shared, int n_parts, size_t part_stride, const float* __restrict__ sgate,
-                   float* __restrict__ out, int D) {
+                   float* __restrict__ out, int D, const int* __restrict__ idx, int E_real, const TH* __restrict__ h) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float acc = 0.f;
-    for (int k = 0; k < top; k++)
-      acc = fmaf(wt[(size_t)t * top + k], y[(size_t)place[(size_t)t * top + k] * D + i], acc);
+    for (int k = 0; k < top; k++) {
+      const size_t p = (size_t)t * top + k;
+      const float v = (idx && idx[p] >= E_real) ? to_float(h[(size_t)t * D + i]) : y[(size_t)place[p] * D + i];
+      acc = fmaf(wt[p], v, acc);
+    }
     if (shared) {
       float s = to_float(shared[(size_t)t * D + i]);
       for (int p = 1; p < n_parts; p++) s += to_float(shared[p * part_stride + (size_t)t * D + i]);
-      acc = fmaf(sgate[t], s, acc);
+      acc = sgate ? fmaf(sgate[t], s, acc) : acc + s;
     }
     out[(size_t)t * D + i] = acc;
   }
@@ -418,7 +461,8 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, c
 // ----------------------------------------------------------------------------- launchers
 // logits: float32 scratch [T, E] (left with the chosen entries at -inf)
 extern "C" int qd_moe_route(const void* h, const void* wr, const float* br, const void* wsg, int dtype, int T, int D,
-                            int E, int top, float* logits, int* idx, float* wt, float* sgate, cudaStream_t stream) {
+                            int E, int top, int mode, const float* corr, float* logits, int* idx, float* wt,
+                            float* sgate, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (top < 1 || top > E || top > MOE_MAX_TOP) return QD_ERR_UNSUPPORTED;
   const int rows = E + (wsg ? 1 : 0);
@@ -432,23 +476,25 @@ extern "C" int qd_moe_route(const void* h, const void* wr, const float* br, cons
   else if (dtype == QD_BF16) { if (al && D % 8 == 0) MR_GO(bf16, true); else MR_GO(bf16, false); }
   else return QD_ERR_UNSUPPORTED;
 #undef MR_GO
-  qd_launch(moe_topk_kernel, dim3((T + 127) / 128), dim3(128), 0, stream, logits, T, E, top, idx, wt);
+  qd_launch(moe_topk_kernel, dim3((T + 127) / 128), dim3(128), 0, stream, logits, T, E, top, mode, corr, idx, wt);
   return qd_last_error();
 }
 
-extern "C" int qd_moe_sort(const int* idx, int n_pairs, int E, int tile_rows, int max_tiles, int* place, int* pair_at,
-                           int* meta, cudaStream_t stream) {
+extern "C" int qd_moe_sort(const int* idx, int n_pairs, int E, int E_real, int tile_rows, int max_tiles, int* place,
+                           int* pair_at, int* meta, cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
   if (E > 4096) return QD_ERR_UNSUPPORTED;
-  qd_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, idx, n_pairs, E, tile_rows,
-            max_tiles, place, pair_at, meta);
+  qd_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, idx, n_pairs, E, E_real,
+            tile_rows, max_tiles, place, pair_at, meta);
   return qd_last_error();
 }
 
 // gated != 0: out[place, N] = silu(A W1_e^T) * (A W2_e^T) in ``out_dtype``; else out = A W1_e^T.
 extern "C" int qd_moe_gemm(const void* A, long long lda, int a_dtype, const int* pair_at, int top, int by_token,
                            const void* W1, const void* W2, int w_dtype, void* out, int out_dtype, int N, int K,
-                           const int* meta, int E, int tile_rows, int max_tiles, int gated, cudaStream_t stream) {
+                           const int* meta, int E, int tile_rows, int max_tiles, int gated, int act_kind, float act_limit,
+                           float act_alpha, cudaStream_t stream) {
+  const MoeAct act = {act_kind, act_limit, act_alpha};
   if (max_tiles <= 0) return 0;
   if (max_tiles > 65535 || (tile_rows != 8 && tile_rows != 16 && tile_rows != 64)) return QD_ERR_UNSUPPORTED;
   dim3 grid((N + 63) / 64, max_tiles);
@@ -463,7 +509,7 @@ extern "C" int qd_moe_gemm(const void* A, long long lda, int a_dtype, const int*
     if (smem > 48 * 1024)                                                                                            \
       cudaFuncSetAttribute(moe_gemv_kernel<TI, TW, TO, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
     qd_launch(moe_gemv_kernel<TI, TW, TO, G>, grid, dim3(256), smem, stream, (const TI*)A, lda, pair_at, top, by_token, \
-              (const TW*)W1, (const TW*)W2, (TO*)out, N, K, meta, E);                                                \
+              (const TW*)W1, (const TW*)W2, (TO*)out, N, K, meta, E, act);                                                \
   } while (0)
 #define MG_PICK(TI, TW, TO) do { if (gated) MG_GO(TI, TW, TO, true); else MG_GO(TI, TW, TO, false); } while (0)
     if (a_dtype == QD_F32 && w_dtype == QD_F32 && out_dtype == QD_F32) MG_PICK(float, float, float);
@@ -478,7 +524,7 @@ extern "C" int qd_moe_gemm(const void* A, long long lda, int a_dtype, const int*
     // many rows per expert in bfloat16: tensor cores
 #define MM_GO(TO, G)                                                                                              \
   qd_launch(moe_gemm_mma_kernel<TO, G>, grid, dim3(128), 0, stream, (const bf16*)A, lda, pair_at, top, by_token,  \
-            (const bf16*)W1, (const bf16*)W2, (TO*)out, N, K, meta, E)
+            (const bf16*)W1, (const bf16*)W2, (TO*)out, N, K, meta, E, act)
     if (out_dtype == QD_BF16) { if (gated) MM_GO(bf16, true); else MM_GO(bf16, false); }
     else if (out_dtype == QD_F32) { if (gated) MM_GO(float, true); else MM_GO(float, false); }
     else return QD_ERR_UNSUPPORTED;
@@ -487,7 +533,7 @@ extern "C" int qd_moe_gemm(const void* A, long long lda, int a_dtype, const int*
   }
 #define MOE_GO(TI, TW, TO, TM, G)                                                                                   \
   qd_launch(moe_gemm_kernel<TI, TW, TO, TM, G>, grid, dim3(256), 0, stream, (const TI*)A, lda, pair_at, top, by_token, \
-            (const TW*)W1, (const TW*)W2, (TO*)out, N, K, meta, E)
+            (const TW*)W1, (const TW*)W2, (TO*)out, N, K, meta, E, act)
 #define MOE_PICK(TI, TW, TO)                                                     \
   do {                                                                           \
     if (tile_rows == 16) { if (gated) MOE_GO(TI, TW, TO, 16, true); else MOE_GO(TI, TW, TO, 16, false); } \
@@ -504,15 +550,21 @@ extern "C" int qd_moe_gemm(const void* A, long long lda, int a_dtype, const int*
 
 extern "C" int qd_moe_combine(const float* y, const int* place, const float* wt, int top, const void* shared,
                               int shared_dtype, int n_parts, long long part_stride, const float* sgate, float* out,
-                              int T, int D, cudaStream_t stream) {
+                              int T, int D, const int* idx, int E_real, const void* h, int h_dtype,
+                              cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (shared && shared_dtype == QD_BF16 && n_parts == 1)
-    qd_launch(moe_combine_kernel<bf16>, dim3(T), dim3(256), 0, stream, y, place, wt, top, (const bf16*)shared, 1,
-              (size_t)0, sgate, out, D);
-  else if (!shared || shared_dtype == QD_F32)
-    qd_launch(moe_combine_kernel<float>, dim3(T), dim3(256), 0, stream, y, place, wt, top, (const float*)shared,
-              n_parts, (size_t)part_stride, sgate, out, D);
-  else
+  if (!h) idx = nullptr;
+#define MC_GO(TS, TH, NP, PS)                                                                                      \
+  qd_launch(moe_combine_kernel<TS, TH>, dim3(T), dim3(256), 0, stream, y, place, wt, top, (const TS*)shared, NP,    \
+            (size_t)(PS), sgate, out, D, idx, E_real, (const TH*)h)
+  const bool hb = h && h_dtype == QD_BF16;
+  if (h && h_dtype != QD_BF16 && h_dtype != QD_F32) return QD_ERR_UNSUPPORTED;
+  if (shared && shared_dtype == QD_BF16 && n_parts == 1) {
+    if (hb) MC_GO(bf16, bf16, 1, 0); else MC_GO(bf16, float, 1, 0);
+  } else if (!shared || shared_dtype == QD_F32) {
+    if (hb) MC_GO(float, bf16, n_parts, part_stride); else MC_GO(float, float, n_parts, part_stride);
+  } else
     return QD_ERR_UNSUPPORTED;
+#undef MC_GO
   return qd_last_error();
 }

@@ -1,0 +1,150 @@
+// Row-wise kernels of layers that are not the pre-norm RMSNorm/SwiGLU kind:
+//
+//   tanh norm    out = tanh(alpha * x) * w + b, a norm without statistics; one launch adds what is pending on the
+//                residual sum first (one or two branch outputs, each [T, D] or float32 partial sums [n, T, D]; a
+//                pending output may be one that joins as unit(y) * u, unit(y) = y / sqrt(mean(y^2) + eps)), writes
+//                the sum back, and may write a second norm of the same row (two branches that read the same x)
+//                (no norm asked for: the additions alone); it may also write the new sum as a rounded copy
+//   gated act    out = act(gate, up) of a stacked [T, 2F] product: silu(g) * u, or the clamped form
+//                min(g, L) * sigmoid(a min(g, L)) * (clamp(u, -L, L) + 1)
+//   token gate   out = gelu_tanh(z) * table[token, :], a per-token row of a side table gating a small projection
+//
+// Everything is float32 inside; a row's sums are taken in an order that depends on the row's length only.
+#include "common.cuh"
+#include <math.h>
+
+__device__ __forceinline__ float ld_code(const void* p, int code, size_t i) {
+  return code == QD_F32 ? reinterpret_cast<const float*>(p)[i] : __bfloat162float(reinterpret_cast<const bf16*>(p)[i]);
+}
+__device__ __forceinline__ void st_code(void* p, int code, size_t i, float v) {
+  if (code == QD_F32) reinterpret_cast<float*>(p)[i] = v;
+  else reinterpret_cast<bf16*>(p)[i] = __float2bfloat16_rn(v);
+}
+
+// One pending addend of the residual sum.
+struct Addend {
+  const void* p;        // [n_parts, T, D] (n_parts 1: [T, D]); null: none
+  int dtype, n_parts;
+  const float* unit_w;  // not null: the addend joins as p / sqrt(mean(p^2) + unit_eps) * unit_w[i]
+  float unit_eps;
+};
+
+__device__ __forceinline__ float addend_at(const Addend& a, size_t stride, size_t i) {
+  float v = ld_code(a.p, a.dtype, i);
+  for (int q = 1; q < a.n_parts; q++) v += ld_code(a.p, a.dtype, q * stride + i);
+  return v;
+}
+
+struct TanhNorm {
+  const float *w, *b;   // [D]
+  float alpha;
+  void* out;            // [n_rows, D]; null: this norm is not computed
+  int out_dtype;
+};
+
+// One CTA per output row r (source row s = rows[r] or r): v = x[s] + a0[s] + a1[s]; x[s] = v when write_back;
+// each norm with an ``out`` writes tanh(alpha v) w + b.
+__global__ void __launch_bounds__(256)
+add_tanh_norm_kernel(float* __restrict__ x, Addend a0, Addend a1, TanhNorm n0, TanhNorm n1,
+                     const int* __restrict__ rows, int D, size_t stride, int write_back, void* __restrict__ copy_out,
+                     int copy_dtype) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const size_t s = rows ? (size_t)rows[r] : (size_t)r;
+  float f0 = 1.f, f1 = 1.f;
+  if (a0.p && a0.unit_w) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) { float v = addend_at(a0, stride, s * D + i); ss = fmaf(v, v, ss); }
+    f0 = 1.0f / sqrtf(block_sum(ss, scratch) / (float)D + a0.unit_eps);
+  }
+  if (a1.p && a1.unit_w) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) { float v = addend_at(a1, stride, s * D + i); ss = fmaf(v, v, ss); }
+    f1 = 1.0f / sqrtf(block_sum(ss, scratch) / (float)D + a1.unit_eps);
+  }
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float v = x[s * D + i];
+    if (a0.p) { float d = addend_at(a0, stride, s * D + i); v += a0.unit_w ? d * f0 * a0.unit_w[i] : d; }
+    if (a1.p) { float d = addend_at(a1, stride, s * D + i); v += a1.unit_w ? d * f1 * a1.unit_w[i] : d; }
+    if (write_back) x[s * D + i] = v;
+    if (copy_out) st_code(copy_out, copy_dtype, (size_t)r * D + i, v);
+    if (n0.out) st_code(n0.out, n0.out_dtype, (size_t)r * D + i, fmaf(tanhf(n0.alpha * v), n0.w[i], n0.b[i]));
+    if (n1.out) st_code(n1.out, n1.out_dtype, (size_t)r * D + i, fmaf(tanhf(n1.alpha * v), n1.w[i], n1.b[i]));
+  }
+}
+
+// x [T, D] float32 (updated when write_back).  Addend k: ak [nk, T, D] of dtype code ak_dtype, null for none; with
+// ak_unit_w it joins unit-normalised.  Norm k: wk, bk [D] float32, alphak, outk [n_rows, D] (null: not computed).
+// rows: int32 [n_rows] source rows, or null for all T rows in order.  copy_out [n_rows, D]: the new sum itself in
+// dtype copy_dtype (null: not written).
+extern "C" int qd_add_tanh_norm(float* x, int T, int D,
+                                const void* a0, int a0_dtype, int a0_parts, const float* a0_unit_w, float a0_eps,
+                                const void* a1, int a1_dtype, int a1_parts, const float* a1_unit_w, float a1_eps,
+                                const float* w0, const float* b0, float alpha0, void* out0, int out0_dtype,
+                                const float* w1, const float* b1, float alpha1, void* out1, int out1_dtype,
+                                const int* rows, int n_rows, int write_back, void* copy_out, int copy_dtype,
+                                cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  Addend A0 = {a0, a0_dtype, a0_parts, a0_unit_w, a0_eps}, A1 = {a1, a1_dtype, a1_parts, a1_unit_w, a1_eps};
+  TanhNorm N0 = {w0, b0, alpha0, out0, out0_dtype}, N1 = {w1, b1, alpha1, out1, out1_dtype};
+  qd_launch(add_tanh_norm_kernel, dim3(n_rows), dim3(256), 0, stream, x, A0, A1, N0, N1, rows, D,
+            (size_t)T * D, write_back, copy_out, copy_dtype);
+  return qd_last_error();
+}
+
+// ------------------------------------------------------------------------------------------------ gated activation
+__global__ void __launch_bounds__(256)
+gated_act_kernel(const void* __restrict__ gu, int in_dtype, void* __restrict__ out, int out_dtype, int F, size_t n,
+                 int kind, float limit, float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / F, f = i - t * F;
+    float g = ld_code(gu, in_dtype, t * 2 * F + f), u = ld_code(gu, in_dtype, t * 2 * F + F + f);
+    float v;
+    if (kind == 0) v = g / (1.0f + expf(-g)) * u;
+    else {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      v = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    }
+    st_code(out, out_dtype, i, v);
+  }
+}
+
+extern "C" int qd_gated_act(const void* gate_up, int in_dtype, void* out, int out_dtype, int T, int F, int kind,
+                            float limit, float alpha, cudaStream_t stream) {
+  const size_t n = (size_t)T * F;
+  if (n == 0) return 0;
+  unsigned blocks = (unsigned)((n + 255) / 256 < 65535 ? (n + 255) / 256 : 65535);
+  qd_launch(gated_act_kernel, dim3(blocks), dim3(256), 0, stream, gate_up, in_dtype, out, out_dtype, F, n, kind, limit,
+            alpha);
+  return qd_last_error();
+}
+
+// ------------------------------------------------------------------------------------------------ token gate
+// out[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], j]
+__global__ void __launch_bounds__(256)
+token_gate_kernel(const void* __restrict__ z, int z_dtype, const void* __restrict__ table, int table_dtype,
+                  const int* __restrict__ tokens, void* __restrict__ out, int out_dtype, int W, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / W, j = i - t * W;
+    const float v = ld_code(z, z_dtype, i);
+    const float g = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    st_code(out, out_dtype, i, g * ld_code(table, table_dtype, (size_t)tokens[t] * W + j));
+  }
+}
+
+extern "C" int qd_token_gate(const void* z, int z_dtype, const void* table, int table_dtype, const int* tokens,
+                             void* out, int out_dtype, int T, int W, cudaStream_t stream) {
+  const size_t n = (size_t)T * W;
+  if (n == 0) return 0;
+  unsigned blocks = (unsigned)((n + 255) / 256 < 65535 ? (n + 255) / 256 : 65535);
+  qd_launch(token_gate_kernel, dim3(blocks), dim3(256), 0, stream, z, z_dtype, table, table_dtype, tokens, out,
+            out_dtype, W, n);
+  return qd_last_error();
+}

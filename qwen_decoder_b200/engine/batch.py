@@ -68,6 +68,9 @@ class StepContext:
     # 0 .. num_decode-1 are those, and a mixer may give them to its decode kernel.  0 when not mixed.
     num_decode: int = 0
     decode_max_context: int = 0   # most keys any of them reads
+    # What a layer leaves for later layers of the same step (a mixer whose values later mixers blend with their own):
+    # keyed by a name the parts agree on; refilled by every run of the step, nothing of it outlives the step.
+    shared: dict = field(default_factory=dict)
 
 
 # single tokens first in a mixed step, for the mixers' decode kernels

@@ -820,7 +820,9 @@ def mamba_gate_norm(y: torch.Tensor, u: torch.Tensor, z_off: int, w: torch.Tenso
 
 
 # ------------------------------------------------------------------ routed experts
+ACT_SILU, ACT_CLAMPED = 0, 1     # gated activations: silu(g) * u; the clamped gate (see ``gated_act``)
 MOE_MAX_TOP = 32
+MOE_ROUTE_TOP_SOFTMAX, MOE_ROUTE_SOFTMAX_ALL = 0, 1
 MOE_FEW_ROWS = 8          # rows of one expert that the weight-streaming grouped product takes as one tile
 
 
@@ -835,49 +837,62 @@ def moe_tile_rows(n_pairs: int, E: int, K1: int, K2: int, dtype: torch.dtype) ->
     return 64 if n_pairs >= 32 * E else 16
 
 
-def moe_route(h: torch.Tensor, wr: torch.Tensor, br: torch.Tensor, wsg: Optional[torch.Tensor], top: int,
-              idx: torch.Tensor, wt: torch.Tensor, sgate: Optional[torch.Tensor]) -> None:
-    """idx, wt [T, top]: the ``top`` experts with the largest float32 logits wr h + br and the softmax over those
-    logits; sgate[t] = sigmoid(wsg . h[t]) when a shared expert's gate vector is given."""
+def moe_route(h: torch.Tensor, wr: torch.Tensor, br: Optional[torch.Tensor], wsg: Optional[torch.Tensor], top: int,
+              idx: torch.Tensor, wt: torch.Tensor, sgate: Optional[torch.Tensor], mode: int = MOE_ROUTE_TOP_SOFTMAX,
+              correction: Optional[torch.Tensor] = None) -> None:
+    """idx, wt [T, top] from the float32 logits wr h (+ br).  ``MOE_ROUTE_TOP_SOFTMAX``: the ``top`` largest logits and
+    the softmax over those.  ``MOE_ROUTE_SOFTMAX_ALL``: scores = softmax over all outputs; the ``top`` largest of
+    score + correction are chosen and weigh by their plain scores.  sgate[t] = sigmoid(wsg . h[t]) when a shared
+    expert's gate vector is given."""
     T, D = h.shape
     E = wr.shape[0]
-    assert wr.shape == (E, D) and wr.dtype == h.dtype and br.dtype == torch.float32 and br.numel() == E
+    assert wr.shape == (E, D) and wr.dtype == h.dtype
+    assert br is None or (br.dtype == torch.float32 and br.numel() == E)
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == E)
     assert idx.dtype == torch.int32 and wt.dtype == torch.float32 and idx.shape == wt.shape == (T, top)
     _contig(h, "h"); _contig(wr, "wr")
     logits = torch.empty((T, E), dtype=torch.float32, device=h.device)
     _check(library("moe").qd_moe_route(_ptr(h), _ptr(wr), _ptr(br), _ptr(wsg), _I(dtype_code(h.dtype)), _I(T), _I(D),
-                                       _I(E), _I(top), _ptr(logits), _ptr(idx), _ptr(wt), _ptr(sgate), _stream()),
+                                       _I(E), _I(top), _I(mode), _ptr(correction), _ptr(logits), _ptr(idx), _ptr(wt),
+                                       _ptr(sgate), _stream()),
            "moe_route")
     _launch_count[0] += 1
 
 
 def moe_sort(idx: torch.Tensor, E: int, tile_rows: int, max_tiles: int, place: torch.Tensor, pair_at: torch.Tensor,
-             meta: torch.Tensor) -> None:
+             meta: torch.Tensor, with_weights: Optional[int] = None) -> None:
     """Order the (token, choice) pairs by expert on the device: place[pair], pair_at[place], and ``meta`` =
-    [offsets (E + 1) | number of tiles | (expert, first row, rows) per tile]."""
+    [offsets (E + 1) | number of tiles | (expert, first row, rows) per tile].  Only the first ``with_weights``
+    experts (default: all) get row tiles: the others have no matrices (identity experts)."""
     n = idx.numel()
     assert place.numel() == n and pair_at.numel() == n and meta.numel() >= E + 2 + 3 * max_tiles
-    _check(library("moe").qd_moe_sort(_ptr(idx), _I(n), _I(E), _I(tile_rows), _I(max_tiles), _ptr(place),
-                                      _ptr(pair_at), _ptr(meta), _stream()), "moe_sort")
+    _check(library("moe").qd_moe_sort(_ptr(idx), _I(n), _I(E), _I(E if with_weights is None else with_weights),
+                                      _I(tile_rows), _I(max_tiles), _ptr(place), _ptr(pair_at), _ptr(meta), _stream()),
+           "moe_sort")
 
 
 def moe_gemm(a: torch.Tensor, pair_at: torch.Tensor, top: int, by_token: bool, w1: torch.Tensor,
-             w2: Optional[torch.Tensor], out: torch.Tensor, meta: torch.Tensor, tile_rows: int, max_tiles: int) -> None:
-    """Grouped product over the sorted pairs: out[place] = a_row W1[e]^T (or, with w2, silu(a W1[e]^T) * (a W2[e]^T));
-    a_row = a[token of the pair] when ``by_token`` else a[place]; w [E, N, K]."""
+             w2: Optional[torch.Tensor], out: torch.Tensor, meta: torch.Tensor, tile_rows: int, max_tiles: int,
+             num_outputs: Optional[int] = None, act: int = ACT_SILU, limit: float = 0.0, alpha: float = 1.0) -> None:
+    """Grouped product over the sorted pairs: out[place] = a_row W1[e]^T (or, with w2, act(a W1[e]^T, a W2[e]^T):
+    silu(g) * u, or the clamped gate of ``gated_act``); a_row = a[token of the pair] when ``by_token`` else a[place];
+    w [E, N, K].  ``num_outputs``: how many outputs the router has (``meta`` is laid out by it), if more than E."""
     E, N, K = w1.shape
     assert a.shape[1] == K and a.stride(1) == 1 and out.shape[1] == N and (w2 is None or w2.shape == w1.shape)
     _contig(w1, "w1"); _contig(out, "out")
     _check(library("moe").qd_moe_gemm(
         _ptr(a), _LL(a.stride(0)), _I(dtype_code(a.dtype)), _ptr(pair_at), _I(top), _I(1 if by_token else 0), _ptr(w1),
-        _ptr(w2), _I(dtype_code(w1.dtype)), _ptr(out), _I(dtype_code(out.dtype)), _I(N), _I(K), _ptr(meta), _I(E),
-        _I(tile_rows), _I(max_tiles), _I(1 if w2 is not None else 0), _stream()), "moe_gemm")
+        _ptr(w2), _I(dtype_code(w1.dtype)), _ptr(out), _I(dtype_code(out.dtype)), _I(N), _I(K), _ptr(meta),
+        _I(E if num_outputs is None else num_outputs), _I(tile_rows), _I(max_tiles), _I(1 if w2 is not None else 0),
+        _I(act), _F(limit), _F(alpha), _stream()), "moe_gemm")
 
 
 def moe_combine(y: torch.Tensor, place: torch.Tensor, wt: torch.Tensor, shared: Optional[torch.Tensor],
-                sgate: Optional[torch.Tensor], out: torch.Tensor) -> None:
+                sgate: Optional[torch.Tensor], out: torch.Tensor, idx: Optional[torch.Tensor] = None,
+                with_weights: int = 0, h: Optional[torch.Tensor] = None) -> None:
     """out[t] = sum_k wt[t, k] y[place[t, k]] + sgate[t] * shared[t] (shared [T, D], or float32 partial sums
-    [n, T, D]); out float32."""
+    [n, T, D]; without ``sgate`` the shared expert counts in full); out float32.  With ``idx`` and ``h``: a pair
+    whose expert index is ``with_weights`` or more is an identity expert and contributes wt * h[t]."""
     T, D = out.shape
     top = wt.shape[1]
     assert y.dtype == torch.float32 and out.dtype == torch.float32 and y.shape[1] == D
@@ -887,9 +902,124 @@ def moe_combine(y: torch.Tensor, place: torch.Tensor, wt: torch.Tensor, shared: 
             n_parts, stride = shared.shape[0], T * D
             assert shared.dtype == torch.float32
         _contig(shared, "shared")
+    if h is not None:
+        assert idx is not None and idx.dtype == torch.int32 and h.shape == (T, D)
+        _contig(h, "h")
     _check(library("moe").qd_moe_combine(
         _ptr(y), _ptr(place), _ptr(wt), _I(top), _ptr(shared), _I(dtype_code(shared.dtype) if shared is not None else 0),
-        _I(n_parts), _LL(stride), _ptr(sgate), _ptr(out), _I(T), _I(D), _stream()), "moe_combine")
+        _I(n_parts), _LL(stride), _ptr(sgate), _ptr(out), _I(T), _I(D), _ptr(idx if h is not None else None),
+        _I(with_weights), _ptr(h), _I(dtype_code(h.dtype) if h is not None else 0), _stream()), "moe_combine")
+
+
+# ------------------------------------------------------------------ tanh norm, gated activations, token gate
+def add_tanh_norm(x: torch.Tensor, addends, norms, rows: Optional[torch.Tensor] = None, write_back: bool = True,
+                  copy_out: Optional[torch.Tensor] = None) -> None:
+    """One launch over the rows of the residual sum x (float32 [T, D]): v = x + the pending ``addends``; x = v when
+    ``write_back``; every norm (w, b, alpha, out) of ``norms`` writes out = tanh(alpha v) w + b; ``copy_out`` gets v
+    itself in its own dtype.  ``addends``: up to two of (tensor [T, D] or float32 partial sums [n, T, D], unit) where
+    unit is None or (u float32 [D], eps): the addend then joins as a / sqrt(mean(a^2) + eps) * u.  ``rows`` (int32):
+    only these rows, outputs in their order."""
+    T, D = x.shape
+    assert x.dtype == torch.float32 and len(addends) <= 2 and len(norms) <= 2
+    _contig(x, "x")
+    n_rows = T if rows is None else rows.numel()
+    args = [_ptr(x), _I(T), _I(D)]
+    for k in range(2):
+        if k < len(addends):
+            a, unit = addends[k]
+            parts = a.shape[0] if a.dim() == 3 else 1
+            assert tuple(a.shape[-2:]) == (T, D) and (parts == 1 or a.dtype == torch.float32)
+            _contig(a, "addend")
+            uw, ue = unit if unit is not None else (None, 0.0)
+            assert uw is None or (uw.dtype == torch.float32 and uw.numel() == D)
+            args += [_ptr(a), _I(dtype_code(a.dtype)), _I(parts), _ptr(uw), _F(ue)]
+        else:
+            args += [_ptr(None), _I(0), _I(1), _ptr(None), _F(0.0)]
+    for k in range(2):
+        if k < len(norms):
+            w, b, alpha, out = norms[k]
+            assert w.dtype == b.dtype == torch.float32 and w.numel() == b.numel() == D and out.shape == (n_rows, D)
+            _contig(out, "out")
+            args += [_ptr(w), _ptr(b), _F(alpha), _ptr(out), _I(dtype_code(out.dtype))]
+        else:
+            args += [_ptr(None), _ptr(None), _F(0.0), _ptr(None), _I(0)]
+    if copy_out is not None:
+        assert copy_out.shape == (n_rows, D)
+        _contig(copy_out, "copy_out")
+    args += [_ptr(rows), _I(n_rows), _I(1 if write_back else 0), _ptr(copy_out),
+             _I(dtype_code(copy_out.dtype) if copy_out is not None else 0), _stream()]
+    _check(library("norm_act").qd_add_tanh_norm(*args), "add_tanh_norm")
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: int = ACT_SILU, limit: float = 0.0,
+              alpha: float = 1.0) -> None:
+    """out[t, f] = act(g, u), g = gate_up[t, f], u = gate_up[t, F + f].  ``ACT_SILU``: silu(g) * u.  ``ACT_CLAMPED``:
+    g' = min(g, limit), u' = clamp(u, -limit, limit), g' * sigmoid(alpha * g') * (u' + 1)."""
+    T, F = out.shape
+    assert gate_up.shape == (T, 2 * F)
+    _contig(gate_up, "gate_up"); _contig(out, "out")
+    _check(library("norm_act").qd_gated_act(_ptr(gate_up), _I(dtype_code(gate_up.dtype)), _ptr(out),
+                                            _I(dtype_code(out.dtype)), _I(T), _I(F), _I(act), _F(limit), _F(alpha),
+                                            _stream()), "gated_act")
+
+
+def token_gate(z: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], j]; z, out [T, W], table [vocab, W]."""
+    T, W = z.shape
+    assert out.shape == (T, W) and table.shape[1] == W and tokens.dtype == torch.int32
+    _contig(z, "z"); _contig(table, "table"); _contig(out, "out")
+    _check(library("norm_act").qd_token_gate(_ptr(z), _I(dtype_code(z.dtype)), _ptr(table), _I(dtype_code(table.dtype)),
+                                             _ptr(tokens), _ptr(out), _I(dtype_code(out.dtype)), _I(T), _I(W),
+                                             _stream()), "token_gate")
+
+
+# ------------------------------------------------------------------ attention with a sink
+def qk_norm_rope_write(qkv: torch.Tensor, H: int, G: int, d: int, vd: int, wq: Optional[torch.Tensor],
+                       wk: Optional[torch.Tensor], eps: float, rotary_dim: int, pairing: int,
+                       cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor,
+                       q_out: torch.Tensor, kv: torch.Tensor, slot_map: torch.Tensor, page_size: int, write_kv: bool,
+                       v_source: Optional[torch.Tensor] = None, lam: Optional[torch.Tensor] = None) -> None:
+    """From qkv [T, H*d + G*d + G*vd] (float32 or bfloat16): q and k unit-normalised per head times wq / wk (float32
+    [d]; None: no norm), their first ``rotary_dim`` elements turned by the table rows of ``positions``; q to q_out
+    [T, H*d], k and v to the token's slot of ``kv`` (pages of [G, page_size, d] keys then [G, page_size, vd] values).
+    With ``v_source`` ([T, G*vd], rows may be strided; same dtype as qkv) and ``lam`` (float32, one number on the
+    device): the values written are (1 - lam) v + lam v_source."""
+    T = qkv.shape[0]
+    assert qkv.shape[1] == H * d + G * d + G * vd and qkv.stride(1) == 1 and positions.dtype == torch.int32
+    assert q_out.shape == (T, H * d) and q_out.is_contiguous()
+    assert (wq is None) == (wk is None) and (wq is None or (wq.dtype == wk.dtype == torch.float32 and wq.numel() == d))
+    if rotary_dim:
+        assert cos.dtype == sin.dtype == torch.float32 and cos.shape[1] == rotary_dim // 2
+    if write_kv:
+        assert kv.numel() % (G * page_size * (d + vd)) == 0 and slot_map.dtype == torch.int32
+        _contig(kv, "kv")
+    if v_source is not None:
+        assert v_source.dtype == qkv.dtype and v_source.shape == (T, G * vd) and v_source.stride(1) == 1
+        assert lam is not None and lam.dtype == torch.float32 and lam.numel() == 1
+    _check(library("attention_sink").qd_qk_norm_rope_write(
+        _ptr(qkv), _I(dtype_code(qkv.dtype)), _LL(qkv.stride(0)), _I(T), _I(H), _I(G), _I(d), _I(vd), _ptr(wq), _ptr(wk),
+        _F(eps), _I(rotary_dim), _I(pairing), _ptr(cos), _ptr(sin), _ptr(positions), _ptr(q_out),
+        _I(dtype_code(q_out.dtype)), _ptr(kv), _I(dtype_code(kv.dtype)), _ptr(slot_map), _I(page_size),
+        _I(1 if write_kv else 0), _ptr(v_source), _LL(v_source.stride(0) if v_source is not None else 0), _ptr(lam),
+        _stream()), "qk_norm_rope_write")
+
+
+def sink_attention_generic(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_table: torch.Tensor,
+                           token_req: torch.Tensor, positions: torch.Tensor, H: int, G: int, d: int, vd: int,
+                           page_size: int, scale: float, window: int, sinks: Optional[torch.Tensor]) -> None:
+    """Attention of every token over keys 0..pos (or the last ``window``) of its request with a sink in the softmax's
+    denominator (``sinks`` float32 [H], or None), values of size ``vd``; q [T, H*d], out [T, H*vd]; float32
+    arithmetic, any sizes."""
+    T = q.shape[0]
+    assert q.shape == (T, H * d) and out.shape == (T, H * vd) and q.dtype == out.dtype == kv.dtype
+    assert kv.numel() % (G * page_size * (d + vd)) == 0
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == H)
+    _contig(q, "q"); _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
+    _check(library("attention_sink").qd_sink_attention_generic(
+        _ptr(q), _LL(q.stride(0)), _ptr(out), _LL(out.stride(0)), _ptr(kv), _I(dtype_code(q.dtype)), _ptr(block_table),
+        _I(block_table.shape[1]), _ptr(token_req), _ptr(positions), _I(T), _I(H), _I(G), _I(d), _I(vd), _I(page_size),
+        _F(scale), _I(window), _ptr(sinks), _stream()), "sink_attention_generic")
 
 
 # ------------------------------------------------------------------ the layers of a prompt step from native code

@@ -48,24 +48,57 @@ class Part:
 
 class ResidualStream:
     """The residual sum of a step: ``x`` float32 [T, D], and a branch output ``delta`` that has
-    not been added yet (the next norm adds it in the same kernel that normalises)."""
+    not been added yet (the next norm's kernel adds it).  Blocks whose two branches read the same
+    x leave a second output pending too (``delta2``), and a pending output may be one that joins
+    unit-normalised: ``delta_unit`` = (u float32 [D], eps) means x += delta / sqrt(mean(delta^2) + eps) * u.
+    A norm that takes only the plain form calls ``settle()`` first."""
 
     def __init__(self, x: torch.Tensor):
         self.x = x
         self.delta: Optional[torch.Tensor] = None
         self.delta_scale: Optional[torch.Tensor] = None     # float32 [D]: a layer scale on the pending branch
+        self.delta_unit = None                              # (u, eps): the pending branch joins unit-normalised
+        self.delta2: Optional[torch.Tensor] = None          # a second pending branch (plain)
 
-    def push(self, delta: torch.Tensor, scale: Optional[torch.Tensor] = None) -> None:
-        """Hand over a branch output (times ``scale`` along D, if given); a delta still pending is added first."""
+    def push(self, delta: torch.Tensor, scale: Optional[torch.Tensor] = None, unit=None) -> None:
+        """Hand over a branch output (times ``scale`` along D, if given); what is still pending is added first."""
         self.flush()
         self.delta = delta
         self.delta_scale = scale
+        self.delta_unit = unit
+
+    def push_pair(self, delta: torch.Tensor, delta2: torch.Tensor) -> None:
+        """Hand over the outputs of two branches that read the same x."""
+        self.flush()
+        self.delta, self.delta2 = delta, delta2
+
+    def pending(self):
+        """The pending outputs as (tensor, unit) pairs, for a kernel that adds up to two of them."""
+        out = []
+        if self.delta is not None:
+            out.append((self.delta, self.delta_unit))
+        if self.delta2 is not None:
+            out.append((self.delta2, None))
+        return out
+
+    def clear(self) -> None:
+        self.delta = self.delta_scale = self.delta_unit = self.delta2 = None
+
+    def settle(self) -> None:
+        """Add what only ``flush`` can add (a second output, a unit-normalised one); a plain pending delta stays."""
+        if self.delta2 is not None or self.delta_unit is not None:
+            self.flush()
 
     def flush(self) -> None:
-        if self.delta is not None:
+        if self.delta is None and self.delta2 is None:
+            return
+        if self.delta2 is None and self.delta_unit is None:
             kernels.residual_add(self.x, self.delta, self.delta_scale)
-            self.delta = None
-            self.delta_scale = None
+        else:
+            if self.delta_scale is not None:
+                raise ValueError("a layer scale on a branch that joins unit-normalised or beside a second branch is not supported")
+            kernels.add_tanh_norm(self.x, self.pending(), [])
+        self.clear()
 
 
 @dataclass

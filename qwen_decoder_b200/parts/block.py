@@ -10,7 +10,9 @@ import torch
 
 from ..config.registry import register_part
 from ..weights.loader import TensorSource, TensorSpec
+from .. import kernels
 from .base import Block, FeedForward, Mixer, Norm, ResidualStream
+from .linear import Linear
 
 
 @register_part("block", "pre_norm")
@@ -105,3 +107,89 @@ class ScaledPreNormBlock(PreNormBlock):
         if self.feed_forward is not None:
             h = self.post_mixer_norm.forward(stream, self.dtype)
             stream.push(self.feed_forward.forward(h, ctx), self.ff_scale)
+
+
+@register_part("block", "parallel_side")
+class ParallelSideBlock(Block):
+    """Two branches that read the same x, then an optional per-layer token input:
+
+        x += mixer(norm1(x)) + feed_forward(norm2(x))                    (a layer may have no feed-forward)
+        e = side_table[token, side_index * side_dim : (side_index + 1) * side_dim]
+        y = Wp (gelu_tanh(Wg x) * e);   x += y / sqrt(mean(y^2) + eps) * ws
+
+    The side table is one tensor for the whole model (``side_table``, [vocab, layers * side_dim]); a block keeps its
+    own slice.  Tensors of the block: ``<prefix>side.gate`` [side_dim, D], ``<prefix>side.proj`` [D, side_dim],
+    ``<prefix>side.norm`` [D].  With ``side_dim`` = 0 the block ends after the two branches.
+
+    Nothing is added to the residual sum by a kernel of its own where the next kernel can do it: the branch outputs
+    wait on the stream for the kernel that needs the new sum (the side input's, which also writes the rounded copy the
+    gate product reads), and the side output waits, to be unit-normalised and added, for the next layer's norms.  When
+    both norms are tanh norms one launch writes both."""
+    norm_roles = ("input", "post_mixer")
+
+    def __init__(self, mixer: Mixer, feed_forward, norms: Dict[str, Norm], size: int, eps: float = 1e-6,
+                 side_dim: int = 0, side_index: int = 0, side_table: str = "side.embed", side_table_shape=None,
+                 prefix: str = ""):
+        if "input" not in norms or (feed_forward is not None and "post_mixer" not in norms):
+            raise ValueError("parallel_side block needs the norms 'input' and, with a feed-forward, 'post_mixer'")
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.norm1, self.norm2 = norms["input"], norms.get("post_mixer") if feed_forward is not None else None
+        self.size, self.eps, self.prefix = size, float(eps), prefix
+        self.side_dim, self.side_index, self.side_table = int(side_dim), int(side_index), side_table
+        self.side_table_shape = tuple(side_table_shape) if side_table_shape else None
+        if self.side_dim:
+            if self.side_table_shape is None or (self.side_index + 1) * self.side_dim > self.side_table_shape[1]:
+                raise ValueError("parallel_side block: the side table has no columns for this layer")
+            self.gate = Linear(size, [(f"{prefix}side.gate", self.side_dim)], bias=False, weight_suffix="")
+            self.proj = Linear(self.side_dim, [(f"{prefix}side.proj", size)], bias=False, weight_suffix="")
+        self.side_rows = self.side_norm = None
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        specs = [s for p in self.parts() for s in p.tensor_specs()]
+        if self.side_dim:
+            specs += self.gate.tensor_specs() + self.proj.tensor_specs()
+            specs += [TensorSpec(f"{self.prefix}side.norm", (self.size,), init="around_one"),
+                      TensorSpec(self.side_table, self.side_table_shape)]      # declared by every layer that reads it
+        return specs
+
+    def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
+        self.dtype = dtype
+        for p in self.parts():
+            p.bind(source, dtype, device)
+        if self.side_dim:
+            self.gate.bind(source, dtype, device)
+            self.proj.bind(source, dtype, device)
+            self.side_norm = source.get(f"{self.prefix}side.norm").to(device=device, dtype=torch.float32).contiguous()
+            lo = self.side_index * self.side_dim
+            self.side_rows = source.get(self.side_table)[:, lo:lo + self.side_dim].to(device=device, dtype=dtype).contiguous()
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        from .norm import TanhNorm
+        T, dev = stream.x.shape[0], stream.x.device
+        n1, n2 = self.norm1, self.norm2
+        if type(n1) is TanhNorm and (n2 is None or type(n2) is TanhNorm) and stream.delta_scale is None:
+            h1 = torch.empty((T, self.size), dtype=self.dtype, device=dev)
+            h2 = torch.empty((T, self.size), dtype=self.dtype, device=dev) if n2 is not None else None
+            kernels.add_tanh_norm(stream.x, stream.pending(),
+                                  [n1.launch_params(h1)] + ([n2.launch_params(h2)] if n2 is not None else []))
+            stream.clear()
+        else:
+            h1 = n1.forward(stream, self.dtype)                      # adds what was pending
+            h2 = n2.forward(stream, self.dtype) if n2 is not None else None
+        a = self.mixer.forward(h1, ctx, cache)
+        if self.feed_forward is not None:
+            stream.push_pair(a, self.feed_forward.forward(h2, ctx))
+        else:
+            stream.push(a)
+        if not self.side_dim:
+            return
+        # the new sum, and its copy in the engine's dtype for the gate product, in one launch
+        xr = torch.empty((T, self.size), dtype=self.dtype, device=dev)
+        kernels.add_tanh_norm(stream.x, stream.pending(), [], copy_out=xr)
+        stream.clear()
+        g = torch.empty((T, self.side_dim), dtype=self.dtype, device=dev)
+        kernels.token_gate(self.gate.forward(xr, out_dtype=torch.float32), self.side_rows, ctx.tokens, g)
+        stream.push(self.proj.forward_partial(g), unit=(self.side_norm, self.eps))

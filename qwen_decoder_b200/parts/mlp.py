@@ -1,6 +1,10 @@
 """SwiGLU feed-forward: h = silu(x W1^T) * (x W3^T); delta = h W2^T, no biases
 (gpu_decoder.cu:457-497, swiglu_kernel gpu_kernels.cu:149-160, cpu_decoder.cpp:204-212;
 W1 = gate_proj, W3 = up_proj, W2 = down_proj).  Gate and up are one stacked product.
+
+``activation`` = "clamped" (with ``limit`` L and ``alpha`` a; the reference has silu only) gates instead with
+g = min(x W1^T, L), u = clamp(x W3^T, -L, L), h = g * sigmoid(a g) * (u + 1); the stacked product then leaves
+float32 sums and one elementwise kernel makes h.
 """
 from __future__ import annotations
 
@@ -16,11 +20,20 @@ from . import matmul_backend
 from .linear import Linear
 
 
+ACTIVATIONS = {"silu": kernels.ACT_SILU, "clamped": kernels.ACT_CLAMPED}
+
+
 @register_part("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "mlp.",
-                 names: Sequence[str] = ("gate_proj", "up_proj", "down_proj"), weight_suffix: str = ".weight"):
+                 names: Sequence[str] = ("gate_proj", "up_proj", "down_proj"), weight_suffix: str = ".weight",
+                 activation: str = "silu", limit: float = 0.0, alpha: float = 1.0):
         """``names``: what the gate, up and down matrices are called after ``prefix``."""
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"gated feed-forward: activation must be one of {sorted(ACTIVATIONS)}, got {activation!r}")
+        if activation == "clamped" and not limit > 0:
+            raise ValueError("gated feed-forward: the clamped activation needs a positive limit")
+        self.activation, self.limit, self.alpha = activation, float(limit), float(alpha)
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
         g, u, d = names
@@ -39,6 +52,8 @@ class SwiGLU(FeedForward):
         self.down.bind(source, dtype, device)
 
     def native_params(self):
+        if self.activation != "silu":
+            return None
         return {"kind": "swiglu", "D": self.hidden_size, "F": self.intermediate_size, "wgu": self.gate_up.weight,
                 "wd": self.down.weight}
 
@@ -48,6 +63,11 @@ class SwiGLU(FeedForward):
             self._barrier.zero_()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        if self.activation != "silu":
+            h = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
+            kernels.gated_act(self.gate_up.forward(x, out_dtype=torch.float32), h, ACTIVATIONS[self.activation],
+                              self.limit, self.alpha)
+            return self.down.forward_partial(h)
         if matmul_backend.mode == "auto" and kernels.ffn_stream_supported(x, self.gate_up.weight, self.down.weight):
             matmul_backend.counters["own"] += 1
             if self._barrier is None:       # this layer's own synchronisation words (zero once; each launch leaves them zero)

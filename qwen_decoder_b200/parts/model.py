@@ -22,7 +22,7 @@ from .base import PagedCacheView, ResidualStream, StateCacheView
 from .linear import Linear
 # importing the part modules registers them
 from . import attention as _attention, block as _block, mlp as _mlp, norm as _norm, rotary as _rotary  # noqa: F401
-from . import latent_attention as _latent, mamba2 as _mamba2, moe as _moe  # noqa: F401
+from . import latent_attention as _latent, mamba2 as _mamba2, moe as _moe, sink_attention as _sink  # noqa: F401
 
 
 class DecoderModel:

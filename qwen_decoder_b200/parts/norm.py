@@ -43,6 +43,7 @@ class RMSNorm(Norm):
 
     def forward(self, stream: ResidualStream, out_dtype: torch.dtype,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        stream.settle()
         n = stream.x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.size), dtype=out_dtype, device=stream.x.device)
         kernels.add_rmsnorm(stream.x, stream.delta, self.weight, out, self.eps, rows=rows,
@@ -50,4 +51,46 @@ class RMSNorm(Norm):
         if rows is None:
             stream.delta = None
             stream.delta_scale = None
+        return out
+
+
+@register_part("norm", "dyntanh")
+class TanhNorm(Norm):
+    """A norm without statistics: out = tanh(alpha * x) * w + b, element by element, with one learned number
+    ``alpha`` and learned vectors w and b (float32 arithmetic).  Tensors: ``<prefix><tensor>`` (w),
+    ``<prefix><tensor>.b``, ``<prefix><tensor>.alpha`` (a scalar).  The kernel adds what is pending on the stream
+    (up to two branch outputs, also one that joins unit-normalised) before it takes the tanh."""
+
+    def __init__(self, size: int, prefix: str = "", tensor: str = "weight"):
+        self.size = size
+        self.prefix = prefix
+        self.tensor = tensor
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+        self.alpha = 1.0
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        n = f"{self.prefix}{self.tensor}"
+        return [TensorSpec(n, (self.size,), init="around_one"), TensorSpec(n + ".b", (self.size,), init="around_zero"),
+                TensorSpec(n + ".alpha", (), init="uniform:0.4:1.2")]
+
+    def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
+        n = f"{self.prefix}{self.tensor}"
+        f32 = lambda name: source.get(name).to(device=device, dtype=torch.float32).contiguous()
+        self.weight, self.bias = f32(n), f32(n + ".b")
+        self.alpha = float(source.get(n + ".alpha").to(torch.float32).reshape(()).item())   # read once, at load time
+
+    def launch_params(self, out: torch.Tensor):
+        return (self.weight, self.bias, self.alpha, out)
+
+    def forward(self, stream: ResidualStream, out_dtype: torch.dtype,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if stream.delta_scale is not None:
+            stream.flush()
+        n = stream.x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.size), dtype=out_dtype, device=stream.x.device)
+        kernels.add_tanh_norm(stream.x, stream.pending(), [self.launch_params(out)], rows=rows,
+                              write_back=rows is None)
+        if rows is None:
+            stream.clear()
         return out

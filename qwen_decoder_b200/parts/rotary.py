@@ -6,6 +6,11 @@ angle theta_p * pos, and rotates the adjacent pair (2p, 2p+1) of every q and k h
 float32 table [positions, rotary_dim / 2], made once from angles taken in float64,
 and the rotation is fused with the cache write (``csrc/elementwise.cu``).
 ``pairing`` = "adjacent" is the reference's; "half" pairs (p, p + rotary_dim / 2).
+
+``scaling`` (the reference has none) stretches the slow pairs for contexts longer than the ``original`` one: with
+c(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln base), lo = max(floor(c(fast)), 0), hi = min(ceil(c(slow)),
+rotary_dim - 1) and r_p = clamp((p - lo) / max(hi - lo, 0.001), 0, 1), pair p turns at
+theta_p / factor * r_p + theta_p * (1 - r_p), and every cosine and sine is multiplied by 0.1 ln(factor) + 1.
 """
 from __future__ import annotations
 
@@ -21,7 +26,7 @@ PAIRING_CODES = {"adjacent": 0, "half": 1}
 
 @register_part("position", "rotary")
 class Rotary(PositionEncoding):
-    def __init__(self, head_dim: int, rotary_dim: int, base: float, pairing: str = "adjacent"):
+    def __init__(self, head_dim: int, rotary_dim: int, base: float, pairing: str = "adjacent", scaling=None):
         if pairing not in PAIRING_CODES:
             raise ValueError(f"rotary pairing must be one of {sorted(PAIRING_CODES)}, got {pairing!r}")
         if rotary_dim % 2 or not (0 < rotary_dim <= head_dim):
@@ -31,12 +36,27 @@ class Rotary(PositionEncoding):
         self.base = float(base)
         self.pairing = pairing
         self.pairing_code = PAIRING_CODES[pairing]
+        if scaling is not None:
+            scaling = {k: float(scaling[k]) for k in ("factor", "original", "fast", "slow")}
+            if scaling["factor"] <= 0 or scaling["original"] <= 0 or scaling["fast"] <= 0 or scaling["slow"] <= 0:
+                raise ValueError("rotary scaling: factor, original, fast and slow must be positive")
+        self.scaling = scaling
         self.cos: Optional[torch.Tensor] = None
         self.sin: Optional[torch.Tensor] = None
 
     def prepare(self, max_positions: int, device: torch.device) -> None:
         p = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
         inv_freq = 1.0 / torch.pow(torch.tensor(self.base, dtype=torch.float64), 2.0 * p / self.rotary_dim)
+        magnitude = 1.0
+        if self.scaling is not None:
+            import math
+            sc = self.scaling
+            turns = lambda t: self.rotary_dim * math.log(sc["original"] / (2.0 * math.pi * t)) / (2.0 * math.log(self.base))
+            lo = max(math.floor(turns(sc["fast"])), 0)
+            hi = min(math.ceil(turns(sc["slow"])), self.rotary_dim - 1)
+            ramp = torch.clamp((p - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            inv_freq = inv_freq / sc["factor"] * ramp + inv_freq * (1.0 - ramp)
+            magnitude = 0.1 * math.log(sc["factor"]) + 1.0
         angle = torch.arange(max_positions, dtype=torch.float64)[:, None] * inv_freq[None, :]
-        self.cos = angle.cos().to(torch.float32).to(device).contiguous()
-        self.sin = angle.sin().to(torch.float32).to(device).contiguous()
+        self.cos = (angle.cos() * magnitude).to(torch.float32).to(device).contiguous()
+        self.sin = (angle.sin() * magnitude).to(torch.float32).to(device).contiguous()
