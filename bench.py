@@ -266,8 +266,39 @@ def hybrid_configs(size):
     return hybrid, dense_cfg
 
 
-def hybrid_bench(args):
-    """``--micro hybrid``: decode steps (batch 1, 8, 64 at ``--context``) and a prompt of ``--prefill-tokens`` tokens, for the
+# ---- Veterax beside the dense decoder at equal layer sizes ---------------------------------------------------------
+# Every layer: sink attention (values smaller than keys) and routed experts with identity outputs and a shared expert, plus
+# the per-layer token input.  "dense": the dense decoder with the same width, depth, heads, head size and vocabulary, and a
+# feed-forward as wide as what a Veterax token uses (its chosen experts and the shared one).
+VETERAX_SIZES = {
+    "S": dict(width=2048, vocab=32000, layers=8, heads=(16, 2), dim=128, vdim=96, side=256,
+              moe=dict(experts=64, identity=8, top=6, ff=1408, shared=2816)),
+    "M": dict(width=4096, vocab=32000, layers=8, heads=(32, 8), dim=128, vdim=128, side=256,
+              moe=dict(experts=32, identity=4, top=4, ff=2048, shared=4096)),
+}
+
+
+def veterax_configs(size):
+    from qwen_decoder_b200.config import config_from_dict
+    z = VETERAX_SIZES[size]
+    H, G = z["heads"]
+    m = z["moe"]
+    mixer = {"heads": H, "kv_heads": G, "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5, "v_mix": True,
+             "rot": {"base": 500000.0, "dims": z["dim"], "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    mlp = {"kind": "moe", "expert": {"ff": m["ff"], "limit": 7.0}, "router": {"experts": m["experts"], "identity": m["identity"],
+           "top": m["top"]}, "shared": {"ff": m["shared"], "limit": 7.0}}
+    veterax = config_from_dict({"architecture": "Veterax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+                                "token_side": {"dim": z["side"]},
+                                "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(z["layers"])]})
+    dense_cfg = config_from_dict(dict(
+        architectures=["Qwen2ForCausalLM"], hidden_size=z["width"], intermediate_size=m["top"] * m["ff"] + m["shared"],
+        num_hidden_layers=z["layers"], num_attention_heads=H, num_key_value_heads=G, head_dim=z["dim"], vocab_size=z["vocab"],
+        max_position_embeddings=32768, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False))
+    return veterax, dense_cfg
+
+
+def hybrid_bench(args, label="hybrid", configs=None):
+    """``--micro hybrid`` (and ``--micro veterax``, which passes its own pair of models): decode steps (batch 1, 8, 64 at ``--context``) and a prompt of ``--prefill-tokens`` tokens, for the
     hybrid design and for the dense decoder at equal sizes; one JSON line.  ``--only hybrid|dense`` and ``--phase`` narrow it
     (for a launch list under a profiler)."""
     import torch
@@ -278,13 +309,13 @@ def hybrid_bench(args):
     batches = [int(b) for b in args.points.split(",") if b] if args.phase != "prefill" else []
     if args.phase in ("all", "decode") and args.batch not in batches:
         batches = sorted(set(batches + [args.batch]))
-    out = {"micro": "hybrid", "size": args.hybrid_size, "context": ctxlen, "prefill_tokens": T, "dtype": "bf16",
+    out = {"micro": label, "size": args.hybrid_size, "context": ctxlen, "prefill_tokens": T, "dtype": "bf16",
            "data": "synthetic: random weights, random token ids, random cache contents", "models": {}}
     gen = torch.Generator().manual_seed(1)
     clocks = ClockSampler()
     clocks.start()
-    for name, cfg in zip(("hybrid", "dense"), hybrid_configs(args.hybrid_size)):
-        if args.only and args.only != name:
+    for name, cfg in zip((label, "dense"), (configs or hybrid_configs)(args.hybrid_size)):
+        if args.only and args.only != name and not (args.only == "hybrid" and name == label):
             continue
         max_b = max(batches + [1])
         span = ctxlen + 2 * (W + K) + 64
@@ -410,6 +441,8 @@ def latent_attend_micro(args):
 def micro(args):
     if args.micro == "hybrid":
         return hybrid_bench(args)
+    if args.micro == "veterax":
+        return hybrid_bench(args, "veterax", veterax_configs)
     if args.micro == "latent_attend":
         return latent_attend_micro(args)
     """One kernel alone: W-streaming contraction, decode attention or prefill attention at the 3B sizes."""
@@ -661,7 +694,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--timeline", action="store_true",
                     help="with --micro prefill_attention: print the kernel's own time stamps of one CTA (microseconds) to stderr")
-    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention", "serve", "mixed_step", "hybrid", "latent_attend"],
+    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention", "serve", "mixed_step", "hybrid", "latent_attend", "veterax"],
                     help="time one kernel alone at the 3B shape (for profiles/), or with 'serve' a whole run of "
                          "--batch requests (--context prompt tokens, --steps new tokens each) through the entry "
                          "point; print one JSON line and exit")
@@ -673,8 +706,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--micro-graph", action="store_true", help="gemm: time inside a replayed graph, cold weights")
     ap.add_argument("--micro-splits", type=int, default=1, help="gemm with --micro-graph: shares of K (partial sums)")
-    ap.add_argument("--hybrid-size", default="S", choices=["S", "M"], help="hybrid: which layer sizes")
-    ap.add_argument("--only", default=None, choices=["hybrid", "dense"], help="hybrid: one of the two models")
+    ap.add_argument("--hybrid-size", default="S", choices=["S", "M"], help="hybrid, veterax: which layer sizes")
+    ap.add_argument("--only", default=None, choices=["hybrid", "dense"], help="hybrid, veterax: one of the two models (hybrid = the first)")
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill"], help="hybrid: decode steps, the prompt, or both")
     ap.add_argument("--history", type=int, default=2048, help="mixed_step: cached tokens before the prompt portion")
     ap.add_argument("--stamps", action="store_true",

@@ -235,3 +235,314 @@ extern "C" int qd_sink_attention_generic(const void* q, long long q_stride, void
     return QD_ERR_UNSUPPORTED;
   return qd_last_error();
 }
+
+// ------------------------------------------------------------------------------------------------ tensor cores
+// The same attention in bfloat16 on mma.sync m16n8k16 (float32 sums), for prompt portions and decoded tokens alike.
+// A CTA of four warps owns one tile of 64 rows of one (request, kv head): rows are (token, head within the group)
+// pairs, 64 / group tokens of them, so every row reads the same keys and values, which arrive in tiles of 64 keys by
+// 16-byte cp.async (two stages) through the block table, key by key: any page size.  Scores stay float32; a softmax
+// weight enters P V as TWO bfloat16 numbers (p = hi + lo, two products into one float32 sum), so weights keep 16 bits
+// of mantissa.  Head sizes are padded with zero columns in shared memory up to the template's D (keys) and DV
+// (values): any multiple of 8 up to 128 runs.  With ``splits`` > 1 the key tiles of a CTA's range are shared among
+// gridDim.z CTAs that leave (o, m, l) per row in scratch memory for ``sink_combine_kernel``, which also adds the
+// sink; with one split the kernel finishes the rows itself.
+#define TS_ROWS 64
+#define TS_KEYS 64
+#define TS_PAD 8
+
+__device__ __forceinline__ void ts_cp_async16(void* smem, const void* gmem, int src_bytes) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(src_bytes));
+}
+__device__ __forceinline__ void ts_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void ts_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ts_ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ts_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned ts_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+// p = hi + lo with hi, lo bfloat16: the packed hi parts of (x, y) and the packed remainders
+__device__ __forceinline__ void ts_split(float x, float y, unsigned& hi, unsigned& lo) {
+  const __nv_bfloat16 hx = __float2bfloat16_rn(x), hy = __float2bfloat16_rn(y);
+  __nv_bfloat162 h; h.x = hx; h.y = hy;
+  hi = *reinterpret_cast<unsigned*>(&h);
+  lo = ts_pack(x - __bfloat162float(hx), y - __bfloat162float(hy));
+}
+__device__ __forceinline__ float ts_quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float ts_quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+template <int D, int DV>
+__global__ void __launch_bounds__(128)
+sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ kv,
+                          const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_tokens,
+                          const int* __restrict__ start_pos, int n_requests, int H, int G, int d, int vd, int page_size,
+                          float scale_log2, int window, const float* __restrict__ sinks, int splits,
+                          float* __restrict__ part_o, float* __restrict__ part_ml) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int KP = D + TS_PAD, VP = DV + TS_PAD;          // row pitches in shared memory (bfloat16)
+  extern __shared__ __align__(16) unsigned char ts_raw[];
+  bf16* Qs = reinterpret_cast<bf16*>(ts_raw);               // [64][KP]
+  bf16* Ks = Qs + TS_ROWS * KP;                             // [2][64][KP]
+  bf16* Vs = Ks + 2 * TS_KEYS * KP;                         // [2][64][VP]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
+  const int gs = H / G, ntok = TS_ROWS / gs;                // tokens of a tile
+  const int g = blockIdx.y, split = blockIdx.z;
+  // which request and which of its tiles
+  int r = 0, b = blockIdx.x, len = 0;
+  for (; r < n_requests; r++) {
+    len = cu_tokens[r + 1] - cu_tokens[r];
+    const int tiles = (len + ntok - 1) / ntok;
+    if (b < tiles) break;
+    b -= tiles;
+  }
+  if (r >= n_requests) return;
+  const int tok0 = b * ntok, toks = min(ntok, len - tok0);  // tokens tok0 .. tok0 + toks - 1 of the request's portion
+  const int t0 = cu_tokens[r] + tok0, pos0 = start_pos[r] + tok0;
+  const int* bt = block_table + (size_t)r * max_blocks;
+  const int key_first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int key_last = pos0 + toks - 1;
+  const int tile_lo = key_first / TS_KEYS, n_tiles_all = key_last / TS_KEYS - tile_lo + 1;
+  const int kt_begin = tile_lo + (int)((long long)n_tiles_all * split / splits);
+  const int kt_end = tile_lo + (int)((long long)n_tiles_all * (split + 1) / splits);
+  const size_t page_elems = (size_t)G * page_size * (d + vd);
+  const size_t k_head = (size_t)g * page_size * d, v_head = (size_t)G * page_size * d + (size_t)g * page_size * vd;
+
+  auto fetch = [&](int kt, int stage) {
+    bf16* ks = Ks + (size_t)stage * TS_KEYS * KP;
+    bf16* vs = Vs + (size_t)stage * TS_KEYS * VP;
+    for (int c = tid; c < TS_KEYS * (D / 8); c += 128) {
+      const int key = c / (D / 8), col = (c - key * (D / 8)) * 8, kidx = kt * TS_KEYS + key;
+      int page = -1;
+      if (kidx >= key_first && kidx <= key_last && col < d) page = bt[kidx / page_size];
+      const bf16* src = page >= 0 ? kv + (size_t)page * page_elems + k_head + (size_t)(kidx % page_size) * d + col : kv;
+      ts_cp_async16(ks + key * KP + col, src, page >= 0 ? 16 : 0);
+    }
+    for (int c = tid; c < TS_KEYS * (DV / 8); c += 128) {
+      const int key = c / (DV / 8), col = (c - key * (DV / 8)) * 8, kidx = kt * TS_KEYS + key;
+      int page = -1;
+      if (kidx >= key_first && kidx <= key_last && col < vd) page = bt[kidx / page_size];
+      const bf16* src = page >= 0 ? kv + (size_t)page * page_elems + v_head + (size_t)(kidx % page_size) * vd + col : kv;
+      ts_cp_async16(vs + key * VP + col, src, page >= 0 ? 16 : 0);
+    }
+  };
+
+  if (kt_begin < kt_end) fetch(kt_begin, 0);
+  ts_commit();
+  // the tile's queries: row = token * gs + head within the group; rows past the tile's tokens and columns past d are zero
+  for (int c = tid; c < TS_ROWS * (D / 8); c += 128) {
+    const int row = c / (D / 8), col = (c - row * (D / 8)) * 8;
+    const int tk = row / gs, hh = row - tk * gs;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tk < toks && col < d)
+      v = *reinterpret_cast<const uint4*>(q + (size_t)(t0 + tk) * H * d + (size_t)(g * gs + hh) * d + col);
+    *reinterpret_cast<uint4*>(Qs + row * KP + col) = v;
+  }
+  __syncthreads();
+  unsigned qa[D / 16][4];
+  {
+    const bf16* q0 = Qs + (warp * 16 + gq) * KP + 2 * tq;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ks++) {
+      qa[ks][0] = *reinterpret_cast<const unsigned*>(q0 + ks * 16);
+      qa[ks][1] = *reinterpret_cast<const unsigned*>(q0 + ks * 16 + 8 * KP);
+      qa[ks][2] = *reinterpret_cast<const unsigned*>(q0 + ks * 16 + 8);
+      qa[ks][3] = *reinterpret_cast<const unsigned*>(q0 + ks * 16 + 8 * KP + 8);
+    }
+  }
+  // this thread's two rows: r0 = warp * 16 + gq, r1 = r0 + 8
+  const int row0 = warp * 16 + gq, row1 = row0 + 8;
+  const int tk0 = row0 / gs, tk1 = row1 / gs;
+  const bool live0 = tk0 < toks, live1 = tk1 < toks;
+  const bool warp_live = warp * 16 < toks * gs;
+  const int p0 = pos0 + tk0, p1 = pos0 + tk1;
+  const int lo0 = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+  const int lo1 = (window > 0 && p1 - window + 1 > 0) ? p1 - window + 1 : 0;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[DV / 8][4];
+#pragma unroll
+  for (int n = 0; n < DV / 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+  for (int kt = kt_begin; kt < kt_end; kt++) {
+    const int stage = (kt - kt_begin) & 1;
+    if (kt + 1 < kt_end) fetch(kt + 1, stage ^ 1);
+    ts_commit();
+    ts_wait<1>();
+    __syncthreads();
+    if (!warp_live) { __syncthreads(); continue; }          // this warp's 16 rows hold no token: it only fetches
+    const bf16* ks_ = Ks + (size_t)stage * TS_KEYS * KP;
+    const bf16* vs_ = Vs + (size_t)stage * TS_KEYS * VP;
+    float s[TS_KEYS / 8][4];
+#pragma unroll
+    for (int n = 0; n < TS_KEYS / 8; n++) {
+      s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      const bf16* kp = ks_ + (n * 8 + gq) * KP + 2 * tq;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ks++)
+        ts_mma(s[n], qa[ks], *reinterpret_cast<const unsigned*>(kp + ks * 16),
+               *reinterpret_cast<const unsigned*>(kp + ks * 16 + 8));
+    }
+    // mask, scale (scores in units of log 2), row maxima
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < TS_KEYS / 8; n++) {
+      const int k0 = kt * TS_KEYS + n * 8 + 2 * tq, k1 = k0 + 1;
+      s[n][0] = (live0 && k0 <= p0 && k0 >= lo0) ? s[n][0] * scale_log2 : -INFINITY;
+      s[n][1] = (live0 && k1 <= p0 && k1 >= lo0) ? s[n][1] * scale_log2 : -INFINITY;
+      s[n][2] = (live1 && k0 <= p1 && k0 >= lo1) ? s[n][2] * scale_log2 : -INFINITY;
+      s[n][3] = (live1 && k1 <= p1 && k1 >= lo1) ? s[n][3] * scale_log2 : -INFINITY;
+      mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+      mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+    }
+    const float mn0 = fmaxf(m0, ts_quad_max(mx0)), mn1 = fmaxf(m1, ts_quad_max(mx1));
+    const float u0 = mn0 == -INFINITY ? 0.f : mn0, u1 = mn1 == -INFINITY ? 0.f : mn1;   // a row with no key yet
+    const float c0 = exp2f(m0 - u0), c1 = exp2f(m1 - u1);
+    m0 = mn0; m1 = mn1;
+    l0 *= c0; l1 *= c1;
+#pragma unroll
+    for (int n = 0; n < DV / 8; n++) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+#pragma unroll
+    for (int n = 0; n < TS_KEYS / 8; n++) {
+      s[n][0] = exp2f(s[n][0] - u0); s[n][1] = exp2f(s[n][1] - u0);
+      s[n][2] = exp2f(s[n][2] - u1); s[n][3] = exp2f(s[n][3] - u1);
+      l0 += s[n][0] + s[n][1];
+      l1 += s[n][2] + s[n][3];
+    }
+    // O += P V, P as hi + lo
+#pragma unroll
+    for (int j = 0; j < TS_KEYS / 16; j++) {
+      unsigned ah[4], al[4];
+      ts_split(s[2 * j][0], s[2 * j][1], ah[0], al[0]);
+      ts_split(s[2 * j][2], s[2 * j][3], ah[1], al[1]);
+      ts_split(s[2 * j + 1][0], s[2 * j + 1][1], ah[2], al[2]);
+      ts_split(s[2 * j + 1][2], s[2 * j + 1][3], ah[3], al[3]);
+#pragma unroll
+      for (int n2 = 0; n2 < DV / 16; n2++) {
+        unsigned vb[4];
+        ts_ldmatrix_x4_trans(vb, vs_ + (j * 16 + (lane & 15)) * VP + n2 * 16 + (lane >> 4) * 8);
+        ts_mma(o[2 * n2], ah, vb[0], vb[1]);
+        ts_mma(o[2 * n2], al, vb[0], vb[1]);
+        ts_mma(o[2 * n2 + 1], ah, vb[2], vb[3]);
+        ts_mma(o[2 * n2 + 1], al, vb[2], vb[3]);
+      }
+    }
+    __syncthreads();          // all warps are done with this stage before the next fetch overwrites it
+  }
+  ts_wait<0>();
+  l0 = ts_quad_sum(l0);
+  l1 = ts_quad_sum(l1);
+#pragma unroll
+  for (int half = 0; half < 2; half++) {
+    const bool live = half ? live1 : live0;
+    if (!live) continue;
+    const int row = half ? row1 : row0, tk = half ? tk1 : tk0;
+    const int h = g * gs + (row - tk * gs), t = t0 + tk;
+    float m = half ? m1 : m0, l = half ? l1 : l0;
+    if (splits > 1) {
+      const size_t pi = ((size_t)t * H + h) * splits + split;
+#pragma unroll
+      for (int n = 0; n < DV / 8; n++) {
+        const int col = n * 8 + 2 * tq;
+        if (col < vd) *reinterpret_cast<float2*>(part_o + pi * vd + col) = make_float2(o[n][2 * half], o[n][2 * half + 1]);
+      }
+      if (tq == 0) { part_ml[pi * 2] = m; part_ml[pi * 2 + 1] = l; }
+      continue;
+    }
+    float c = 1.f;
+    if (sinks) {
+      const float sk = sinks[h] * 1.4426950408889634f, mn = fmaxf(m, sk);
+      c = exp2f(m - mn);
+      l = l * c + exp2f(sk - mn);
+    }
+    const float f = c / l;
+#pragma unroll
+    for (int n = 0; n < DV / 8; n++) {
+      const int col = n * 8 + 2 * tq;
+      if (col < vd)
+        *reinterpret_cast<unsigned*>(out + (size_t)t * H * vd + (size_t)h * vd + col) =
+            ts_pack(o[n][2 * half] * f, o[n][2 * half + 1] * f);
+    }
+  }
+}
+
+// One warp per (token, head): the splits' (o, m, l) and the sink become the output row.
+__global__ void __launch_bounds__(128)
+sink_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ sinks,
+                    bf16* __restrict__ out, int n_rows, int H, int vd, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + warp;                    // t * H + h
+  if (row >= n_rows) return;
+  float M = sinks ? sinks[row % H] * 1.4426950408889634f : -INFINITY;
+  for (int s = 0; s < splits; s++) M = fmaxf(M, part_ml[((size_t)row * splits + s) * 2]);
+  float L = sinks ? exp2f(sinks[row % H] * 1.4426950408889634f - M) : 0.f;
+  for (int s = 0; s < splits; s++) {
+    const float m = part_ml[((size_t)row * splits + s) * 2];
+    if (m != -INFINITY) L += part_ml[((size_t)row * splits + s) * 2 + 1] * exp2f(m - M);
+  }
+  for (int i = lane; i < vd; i += 32) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; s++) {
+      const float m = part_ml[((size_t)row * splits + s) * 2];
+      if (m != -INFINITY) acc += part_o[((size_t)row * splits + s) * vd + i] * exp2f(m - M);
+    }
+    out[(size_t)row * vd + i] = __float2bfloat16_rn(acc / L);
+  }
+}
+
+// q [n_tokens, H * d] and out [n_tokens, H * vd] bfloat16, dense; cu_tokens [n_requests + 1] rows of q / out per
+// request, start_pos [n_requests] the position of each request's first row; block_table [n_requests, max_blocks].
+// tiles: sum over requests of ceil(tokens / (64 / (H / G))) (an upper bound will do).  part_o [n_tokens * H * splits,
+// vd] and part_ml [n_tokens * H * splits, 2] float32 when splits > 1.
+extern "C" int qd_sink_attention_mma(const void* q, void* out, const void* kv, const int* block_table, int max_blocks,
+                                     const int* cu_tokens, const int* start_pos, int n_requests, int n_tokens, int tiles,
+                                     int H, int G, int d, int vd, int page_size, float scale, int window,
+                                     const float* sinks, int splits, float* part_o, float* part_ml,
+                                     cudaStream_t stream) {
+  if (n_tokens <= 0 || n_requests <= 0) return 0;
+  if (G <= 0 || H % G || H / G > TS_ROWS || d <= 0 || vd <= 0 || d > 128 || vd > 128 || d % 8 || vd % 8 ||
+      page_size <= 0 || splits < 1 || splits > 65535 || G > 65535 || (splits > 1 && (!part_o || !part_ml)))
+    return QD_ERR_UNSUPPORTED;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(tiles, G, splits);
+#define TS_GO(D_, DV_)                                                                                              \
+  do {                                                                                                              \
+    const size_t smem = ((size_t)TS_ROWS * (D_ + TS_PAD) + 2 * TS_KEYS * (D_ + TS_PAD) + 2 * TS_KEYS * (DV_ + TS_PAD)) * 2; \
+    static bool raised = false;                                                                                     \
+    if (!raised) {                                                                                                  \
+      cudaFuncSetAttribute(sink_attention_mma_kernel<D_, DV_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      raised = true;                                                                                                \
+    }                                                                                                               \
+    qd_launch(sink_attention_mma_kernel<D_, DV_>, grid, dim3(128), smem, stream, (const bf16*)q, (bf16*)out,          \
+              (const bf16*)kv, block_table, max_blocks, cu_tokens, start_pos, n_requests, H, G, d, vd, page_size,    \
+              scale_log2, window, sinks, splits, part_o, part_ml);                                                   \
+  } while (0)
+  if (d <= 64 && vd <= 64) TS_GO(64, 64);
+  else if (d <= 64) TS_GO(64, 128);
+  else if (vd <= 64) TS_GO(128, 64);
+  else TS_GO(128, 128);
+#undef TS_GO
+  if (splits > 1) {
+    const int rows = n_tokens * H;
+    qd_launch(sink_combine_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, (const float*)part_o,
+              (const float*)part_ml, sinks, (bf16*)out, rows, H, vd, splits);
+  }
+  return qd_last_error();
+}

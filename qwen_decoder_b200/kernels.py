@@ -1022,6 +1022,44 @@ def sink_attention_generic(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor,
         _F(scale), _I(window), _ptr(sinks), _stream()), "sink_attention_generic")
 
 
+SINK_MMA_ROWS = 64       # rows, (token, head within the group) pairs, of one tile of the tensor-core kernel
+
+
+def sink_mma_supported(dtype: torch.dtype, H: int, G: int, d: int, vd: int) -> bool:
+    """What the tensor-core form of the sink attention takes: bfloat16, head sizes that are multiples of 8 up to 128,
+    groups of up to 64 query heads per key/value head; any page size."""
+    return (dtype == torch.bfloat16 and H % G == 0 and H // G <= SINK_MMA_ROWS and d % 8 == 0 and vd % 8 == 0
+            and 0 < d <= 128 and 0 < vd <= 128)
+
+
+def sink_attention_mma(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_table: torch.Tensor,
+                       cu_tokens: torch.Tensor, start_pos: torch.Tensor, n_requests: int, n_tokens: int, H: int, G: int,
+                       d: int, vd: int, page_size: int, scale: float, window: int, sinks: Optional[torch.Tensor],
+                       splits: int = 1) -> None:
+    """``sink_attention_generic`` on tensor cores for portions of ``n_requests`` requests (rows cu_tokens[r] ..
+    cu_tokens[r+1]-1 of q and out, at positions start_pos[r]..): a decoded token is a portion of one.  ``splits`` > 1
+    shares every tile's keys among that many CTAs (for steps of few tokens over long contexts)."""
+    assert q.dtype == out.dtype == kv.dtype == torch.bfloat16 and q.shape[1] == H * d and out.shape[1] == H * vd
+    assert kv.numel() % (G * page_size * (d + vd)) == 0
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.shape[0] >= n_requests
+    assert cu_tokens.dtype == torch.int32 and start_pos.dtype == torch.int32
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == H)
+    _contig(q, "q"); _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
+    ntok = SINK_MMA_ROWS // (H // G)
+    tiles = n_tokens // ntok + n_requests            # at least sum over requests of ceil(tokens / ntok)
+    part_o = part_ml = None
+    if splits > 1:
+        rows = out.shape[0] * H
+        part_o = torch.empty((rows * splits, vd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((rows * splits, 2), dtype=torch.float32, device=q.device)
+    _check(library("attention_sink").qd_sink_attention_mma(
+        _ptr(q), _ptr(out), _ptr(kv), _ptr(block_table), _I(block_table.shape[1]), _ptr(cu_tokens), _ptr(start_pos),
+        _I(n_requests), _I(n_tokens), _I(tiles), _I(H), _I(G), _I(d), _I(vd), _I(page_size), _F(scale), _I(window),
+        _ptr(sinks), _I(splits), _ptr(part_o), _ptr(part_ml), _stream()), "sink_attention_mma")
+    if splits > 1:
+        _launch_count[0] += 1
+
+
 # ------------------------------------------------------------------ the layers of a prompt step from native code
 class PromptLayer(ctypes.Structure):
     """One schedule entry of the native prompt step (PeLayer in csrc/prompt_exec.cu)."""

@@ -28,8 +28,12 @@ from .. import kernels
 from ..cache import PagedKV
 from ..config.registry import register_part
 from ..weights.loader import TensorSource, TensorSpec
+from .attention import decode_splits
 from .base import Mixer, PagedCacheView
 from .linear import Linear
+
+import os as _os
+_TENSOR_CORES = _os.environ.get("QD_SINK_MMA", "1") != "0"       # 0: every dtype and size on the float32 kernel
 
 
 @register_part("mixer", "sink_attention")
@@ -106,6 +110,18 @@ class SinkAttention(Mixer):
         kernels.qk_norm_rope_write(qkv, H, G, d, vd, self.w_q_norm, self.w_k_norm, self.eps, *rope, ctx.positions, q,
                                    cache.kv, cache.group.slot_map, ps, cache.write, v_source, self.lam)
         attn = torch.empty((T, H * vd), dtype=x.dtype, device=x.device)
+        if _TENSOR_CORES and kernels.sink_mma_supported(x.dtype, H, G, d, vd):
+            # single tokens (all of the step, or the first ``num_decode`` of a mixed one) share their keys among CTAs
+            args = (H, G, d, vd, ps, self.scale, window, self.sinks)
+            nd = T if ctx.all_decode else getattr(ctx, "num_decode", 0)
+            if nd:
+                keys = ctx.max_context if ctx.all_decode else ctx.decode_max_context
+                kernels.sink_attention_mma(q, attn, cache.kv, cache.group.block_table, ctx.cu_tokens, ctx.start_pos,
+                                           nd, nd, *args, splits=decode_splits(nd * G, min(keys, window or keys)))
+            if nd < T:
+                kernels.sink_attention_mma(q, attn, cache.kv, cache.group.block_table[nd:], ctx.cu_tokens[nd:],
+                                           ctx.start_pos[nd:], ctx.num_requests - nd, T - nd, *args)
+            return self.out.forward_partial(attn)
         kernels.sink_attention_generic(q, attn, cache.kv, cache.group.block_table, ctx.token_request, ctx.positions,
                                        H, G, d, vd, ps, self.scale, window, self.sinks)
         return self.out.forward_partial(attn)

@@ -125,18 +125,30 @@ def read_outputs(trace: Trace, out_dir: str, vocab: int) -> Dict[int, np.ndarray
     return out
 
 
-def compare(trace: Trace, got: Dict[int, np.ndarray], want_logits, rel_tol: float):
+def compare(trace: Trace, got: Dict[int, np.ndarray], want_logits, rel_tol: float, stray: float = 0.0,
+            stray_factor: float = 3.0):
     """Every replayed row against the plain implementation's row; the first wrong place is named.
-    ``want_logits[r]`` is indexed by position: an array [positions, vocab] or a dict position -> row."""
+    ``want_logits[r]`` is indexed by position: an array [positions, vocab] or a dict position -> row.
+    ``stray``: the share of rows (at least one, if positive) that may lie above the tolerance, though never above
+    ``stray_factor`` times it: a bfloat16 run of a design that divides a projection's output by its own length
+    meets, now and then, a token whose output is short by cancellation, and the rounding of its input then weighs
+    many times as much as elsewhere."""
     def largest(w):
         return max(float(np.abs(v).max()) for v in w.values()) if isinstance(w, dict) else float(np.abs(w).max())
     scale = max(largest(w) for w in want_logits)
-    worst = 0.0
+    worst, n_rows, over = 0.0, 0, []
     for s in sorted(trace.expect):
         for i, (r, p) in enumerate(trace.expect[s]):
             err = float(np.abs(got[s][i].astype(np.float64) - want_logits[r][p]).max())
             worst = max(worst, err)
-            assert err <= rel_tol * scale, (
+            n_rows += 1
+            if err > rel_tol * scale:
+                over.append((err, s, i, r, p))
+            assert err <= rel_tol * scale * (stray_factor if stray > 0 else 1.0), (
                 f"step {s} row {i}: request {r} position {p}: max |diff| {err:.3e} > "
                 f"{rel_tol:.1e} * {scale:.3e}")
+    allowed = max(1, int(stray * n_rows)) if stray > 0 else 0
+    assert len(over) <= allowed, (
+        f"{len(over)} of {n_rows} rows above {rel_tol:.1e} * {scale:.3e} (allowed {allowed}); the first: "
+        f"step {over[0][1]} row {over[0][2]}: request {over[0][3]} position {over[0][4]}: {over[0][0]:.3e}")
     return worst / scale
