@@ -242,8 +242,8 @@ extern "C" int qd_sink_attention_generic(const void* q, long long q_stride, void
 // pairs, 64 / group tokens of them, so every row reads the same keys and values, which arrive in tiles of 64 keys by
 // 16-byte cp.async (two stages) through the block table, key by key: any page size.  Scores stay float32; a softmax
 // weight enters P V as TWO bfloat16 numbers (p = hi + lo, two products into one float32 sum), so weights keep 16 bits
-// of mantissa.  Head sizes are padded with zero columns in shared memory up to the template's D (keys) and DV
-// (values): any multiple of 8 up to 128 runs.  With ``splits`` > 1 the key tiles of a CTA's range are shared among
+// of mantissa.  Head sizes are padded with zero columns in shared memory up to the template's D (keys: 64, 128) and DV
+// (values: 64, 96, 128): any multiple of 8 up to 128 runs.  With ``splits`` > 1 the key tiles of a CTA's range are shared among
 // gridDim.z CTAs that leave (o, m, l) per row in scratch memory for ``sink_combine_kernel``, which also adds the
 // sink; with one split the kernel finishes the rows itself.
 #define TS_ROWS 64
@@ -278,6 +278,16 @@ __device__ __forceinline__ void ts_split(float x, float y, unsigned& hi, unsigne
   hi = *reinterpret_cast<unsigned*>(&h);
   lo = ts_pack(x - __bfloat162float(hx), y - __bfloat162float(hy));
 }
+__device__ __forceinline__ float ts_exp2(float x) {          // 2^x, two units in the last place; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void ts_ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
 __device__ __forceinline__ float ts_quad_max(float v) {
   v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
   return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
@@ -293,7 +303,7 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
                           const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_tokens,
                           const int* __restrict__ start_pos, int n_requests, int H, int G, int d, int vd, int page_size,
                           float scale_log2, int window, const float* __restrict__ sinks, int splits,
-                          float* __restrict__ part_o, float* __restrict__ part_ml) {
+                          float* __restrict__ part_o, float* __restrict__ part_ml, int page_shift) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int KP = D + TS_PAD, VP = DV + TS_PAD;          // row pitches in shared memory (bfloat16)
@@ -324,21 +334,28 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
   const size_t page_elems = (size_t)G * page_size * (d + vd);
   const size_t k_head = (size_t)g * page_size * d, v_head = (size_t)G * page_size * d + (size_t)g * page_size * vd;
 
+  // (page, offset in page) of a key: a shift and a mask where the page size is a power of two
+  auto page_of = [&](int kidx, int& off) {
+    if (page_shift >= 0) { off = kidx & (page_size - 1); return bt[kidx >> page_shift]; }
+    const int lp = kidx / page_size;
+    off = kidx - lp * page_size;
+    return bt[lp];
+  };
   auto fetch = [&](int kt, int stage) {
     bf16* ks = Ks + (size_t)stage * TS_KEYS * KP;
     bf16* vs = Vs + (size_t)stage * TS_KEYS * VP;
     for (int c = tid; c < TS_KEYS * (D / 8); c += 128) {
       const int key = c / (D / 8), col = (c - key * (D / 8)) * 8, kidx = kt * TS_KEYS + key;
-      int page = -1;
-      if (kidx >= key_first && kidx <= key_last && col < d) page = bt[kidx / page_size];
-      const bf16* src = page >= 0 ? kv + (size_t)page * page_elems + k_head + (size_t)(kidx % page_size) * d + col : kv;
+      int page = -1, off = 0;
+      if (kidx >= key_first && kidx <= key_last && col < d) page = page_of(kidx, off);
+      const bf16* src = page >= 0 ? kv + (size_t)page * page_elems + k_head + (size_t)off * d + col : kv;
       ts_cp_async16(ks + key * KP + col, src, page >= 0 ? 16 : 0);
     }
     for (int c = tid; c < TS_KEYS * (DV / 8); c += 128) {
       const int key = c / (DV / 8), col = (c - key * (DV / 8)) * 8, kidx = kt * TS_KEYS + key;
-      int page = -1;
-      if (kidx >= key_first && kidx <= key_last && col < vd) page = bt[kidx / page_size];
-      const bf16* src = page >= 0 ? kv + (size_t)page * page_elems + v_head + (size_t)(kidx % page_size) * vd + col : kv;
+      int page = -1, off = 0;
+      if (kidx >= key_first && kidx <= key_last && col < vd) page = page_of(kidx, off);
+      const bf16* src = page >= 0 ? kv + (size_t)page * page_elems + v_head + (size_t)off * vd + col : kv;
       ts_cp_async16(vs + key * VP + col, src, page >= 0 ? 16 : 0);
     }
   };
@@ -392,11 +409,15 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
 #pragma unroll
     for (int n = 0; n < TS_KEYS / 8; n++) {
       s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
-      const bf16* kp = ks_ + (n * 8 + gq) * KP + 2 * tq;
+      // one instruction fetches the key tile's operands of two steps of 16 dimensions
+      const bf16* kp = ks_ + (n * 8 + (lane & 7)) * KP + (lane >> 3) * 8;
 #pragma unroll
-      for (int ks = 0; ks < D / 16; ks++)
-        ts_mma(s[n], qa[ks], *reinterpret_cast<const unsigned*>(kp + ks * 16),
-               *reinterpret_cast<const unsigned*>(kp + ks * 16 + 8));
+      for (int ks = 0; ks < D / 16; ks += 2) {
+        unsigned kb[4];
+        ts_ldmatrix_x4(kb, kp + ks * 16);
+        ts_mma(s[n], qa[ks], kb[0], kb[1]);
+        ts_mma(s[n], qa[ks + 1], kb[2], kb[3]);
+      }
     }
     // mask, scale (scores in units of log 2), row maxima
     float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -412,15 +433,15 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
     }
     const float mn0 = fmaxf(m0, ts_quad_max(mx0)), mn1 = fmaxf(m1, ts_quad_max(mx1));
     const float u0 = mn0 == -INFINITY ? 0.f : mn0, u1 = mn1 == -INFINITY ? 0.f : mn1;   // a row with no key yet
-    const float c0 = exp2f(m0 - u0), c1 = exp2f(m1 - u1);
+    const float c0 = ts_exp2(m0 - u0), c1 = ts_exp2(m1 - u1);
     m0 = mn0; m1 = mn1;
     l0 *= c0; l1 *= c1;
 #pragma unroll
     for (int n = 0; n < DV / 8; n++) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
 #pragma unroll
     for (int n = 0; n < TS_KEYS / 8; n++) {
-      s[n][0] = exp2f(s[n][0] - u0); s[n][1] = exp2f(s[n][1] - u0);
-      s[n][2] = exp2f(s[n][2] - u1); s[n][3] = exp2f(s[n][3] - u1);
+      s[n][0] = ts_exp2(s[n][0] - u0); s[n][1] = ts_exp2(s[n][1] - u0);
+      s[n][2] = ts_exp2(s[n][2] - u1); s[n][3] = ts_exp2(s[n][3] - u1);
       l0 += s[n][0] + s[n][1];
       l1 += s[n][2] + s[n][3];
     }
@@ -481,7 +502,9 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
   }
 }
 
-// One warp per (token, head): the splits' (o, m, l) and the sink become the output row.
+// One warp per (token, head): the splits' (o, m, l) and the sink become the output row.  Lane s holds split s's
+// maximum and sum (up to 64 splits: two per lane); the output elements then add the splits' rows with weights that
+// come by shuffle, so the loads of all splits are independent of one another.
 __global__ void __launch_bounds__(128)
 sink_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ sinks,
                     bf16* __restrict__ out, int n_rows, int H, int vd, int splits) {
@@ -490,20 +513,24 @@ sink_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + warp;                    // t * H + h
   if (row >= n_rows) return;
-  float M = sinks ? sinks[row % H] * 1.4426950408889634f : -INFINITY;
-  for (int s = 0; s < splits; s++) M = fmaxf(M, part_ml[((size_t)row * splits + s) * 2]);
-  float L = sinks ? exp2f(sinks[row % H] * 1.4426950408889634f - M) : 0.f;
-  for (int s = 0; s < splits; s++) {
-    const float m = part_ml[((size_t)row * splits + s) * 2];
-    if (m != -INFINITY) L += part_ml[((size_t)row * splits + s) * 2 + 1] * exp2f(m - M);
-  }
-  for (int i = lane; i < vd; i += 32) {
+  const float2* ml = reinterpret_cast<const float2*>(part_ml) + (size_t)row * splits;
+  const float2 a = lane < splits ? ml[lane] : make_float2(-INFINITY, 0.f);
+  const float2 b = lane + 32 < splits ? ml[lane + 32] : make_float2(-INFINITY, 0.f);
+  const float sk = sinks ? sinks[row % H] * 1.4426950408889634f : -INFINITY;
+  const float M = fmaxf(warp_max(fmaxf(a.x, b.x)), sk);
+  const float wa = a.x == -INFINITY ? 0.f : exp2f(a.x - M), wb = b.x == -INFINITY ? 0.f : exp2f(b.x - M);
+  const float L = warp_sum(a.y * wa + b.y * wb) + (sinks ? exp2f(sk - M) : 0.f);
+  const float inv = 1.0f / L;
+  const float* po = part_o + (size_t)row * splits * vd;
+  for (int i0 = 0; i0 < vd; i0 += 32) {                     // every lane takes every turn: the shuffles need them all
+    const int i = i0 + lane;
     float acc = 0.f;
+#pragma unroll 4
     for (int s = 0; s < splits; s++) {
-      const float m = part_ml[((size_t)row * splits + s) * 2];
-      if (m != -INFINITY) acc += part_o[((size_t)row * splits + s) * vd + i] * exp2f(m - M);
+      const float w = __shfl_sync(0xffffffffu, s < 32 ? wa : wb, s & 31);
+      if (i < vd) acc = fmaf(po[(size_t)s * vd + i], w, acc);
     }
-    out[(size_t)row * vd + i] = __float2bfloat16_rn(acc / L);
+    if (i < vd) out[(size_t)row * vd + i] = __float2bfloat16_rn(acc * inv);
   }
 }
 
@@ -518,9 +545,12 @@ extern "C" int qd_sink_attention_mma(const void* q, void* out, const void* kv, c
                                      cudaStream_t stream) {
   if (n_tokens <= 0 || n_requests <= 0) return 0;
   if (G <= 0 || H % G || H / G > TS_ROWS || d <= 0 || vd <= 0 || d > 128 || vd > 128 || d % 8 || vd % 8 ||
-      page_size <= 0 || splits < 1 || splits > 65535 || G > 65535 || (splits > 1 && (!part_o || !part_ml)))
+      page_size <= 0 || splits < 1 || splits > 64 || G > 65535 || (splits > 1 && (!part_o || !part_ml)))
     return QD_ERR_UNSUPPORTED;
   const float scale_log2 = scale * 1.4426950408889634f;
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (page_shift = 0; (1 << page_shift) < page_size; page_shift++) {}
   dim3 grid(tiles, G, splits);
 #define TS_GO(D_, DV_)                                                                                              \
   do {                                                                                                              \
@@ -532,11 +562,12 @@ extern "C" int qd_sink_attention_mma(const void* q, void* out, const void* kv, c
     }                                                                                                               \
     qd_launch(sink_attention_mma_kernel<D_, DV_>, grid, dim3(128), smem, stream, (const bf16*)q, (bf16*)out,          \
               (const bf16*)kv, block_table, max_blocks, cu_tokens, start_pos, n_requests, H, G, d, vd, page_size,    \
-              scale_log2, window, sinks, splits, part_o, part_ml);                                                   \
+              scale_log2, window, sinks, splits, part_o, part_ml, page_shift);                                       \
   } while (0)
   if (d <= 64 && vd <= 64) TS_GO(64, 64);
   else if (d <= 64) TS_GO(64, 128);
   else if (vd <= 64) TS_GO(128, 64);
+  else if (vd <= 96) TS_GO(128, 96);
   else TS_GO(128, 128);
 #undef TS_GO
   if (splits > 1) {

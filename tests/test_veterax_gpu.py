@@ -75,6 +75,7 @@ ONE_LAYER = {
     "attention_wide_heads": (vc.attn(2, 1, 128, 128, scale=0.05), None, 0, 64),
     "attention_odd_sizes": (vc.attn(3, 3, 10, 6, rot_dims=6), None, 0, 64),
     "attention_many_heads_per_group": (vc.attn(40, 2, 8, 8), None, 0, 64),
+    "attention_values_past_one_warp": (vc.attn(6, 3, 32, 56), None, 0, 64),
     "side_input": (SMALL_MIX, None, 12, 64),
     "side_input_of_one": (SMALL_MIX, PLAIN_FF, 1, 72),
     "experts": (SMALL_MIX, vc.moe(7, 3, 24, 1.5), 0, 64),
@@ -217,7 +218,7 @@ def test_one_far_key_stands_out(dtype, tmp_path):
     that is lost, read from the wrong row of a page, one position off, or turned by the wrong angle changes the logits
     by far more than the tolerance.  Prompts end just before, at and just after page and key-tile borders; the tail is
     decoded token by token, with its keys shared among several CTAs."""
-    cfg = vc.one_layer(vc.attn(4, 2, 16, 24, base=200.0, scaling=vc.yarn(4.0, 64, 16.0, 2.0), scale=1.0), None,
+    cfg = vc.one_layer(vc.attn(4, 2, 16, 40, base=200.0, scaling=vc.yarn(4.0, 64, 16.0, 2.0), scale=1.0), None,
                        vocab=400, width=48)
     # bfloat16 rounds q and the cached keys to 8 bits: scores of this size then move by tenths, and so would the
     # weights of a softmax as sharp as the float32 run's; its run is a little less sharp
@@ -250,6 +251,31 @@ def test_one_far_key_stands_out(dtype, tmp_path):
                             trace_tools.portions(seqs, sizes=(100, 2, 3, 64)))):
         got = trace_tools.run_inprocess(runner, tr, str(tmp_path / f"o{i}"))
         trace_tools.compare(tr, got, want, TOL[dtype], stray=STRAY[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_over_a_long_context(dtype, tmp_path):
+    """A thousand keys behind each decoded token: its keys are shared among many CTAs whose partial results (values of
+    a size that is no multiple of a warp) are added up with the sink; positions around the borders of 64-key tiles."""
+    cfg = vc.one_layer(vc.attn(4, 2, 32, 40, base=5000.0, scale=0.4), vc.moe(3, 2, 16, 2.0, identity=1), vocab=150, width=64)
+    folder = vc.make_folder(cfg, str(tmp_path / "m"), seed=12, std=0.15, edit=vc.steady_routing if dtype == "bfloat16" else None)
+    cfg, w = vc.read_folder(folder)
+    rng = random.Random(2)
+    seqs = [[rng.randrange(cfg["vocab"]) for _ in range(n)] for n in (1030, 1093)]
+    want = [{p: row for p, row in enumerate(x) if p >= 940} for x in expected(cfg, w, seqs)]
+    runner = make_runner(folder, dtype, 2304, page_size=32)
+    tr = trace_tools.decode_tail(seqs, tail=70, keep=lambda r, p: p >= 940)
+    got = trace_tools.run_inprocess(runner, tr, str(tmp_path / "o"))
+    trace_tools.compare(tr, got, want, TOL[dtype], stray=STRAY[dtype])
+    # and both requests decoding side by side
+    tr = trace_tools.Trace()
+    n0 = 1000
+    tr.add([(r, 0, s[:n0], []) for r, s in enumerate(seqs)])
+    for p in range(n0, 1030):
+        tr.add([(r, p, s[p:p + 1], [0]) for r, s in enumerate(seqs)], end=[0, 1] if p == 1029 else [])
+    got = trace_tools.run_inprocess(runner, tr, str(tmp_path / "p"))
+    trace_tools.compare(tr, got, want, TOL[dtype], stray=STRAY[dtype])
+    all_free(runner)
 
 
 def test_the_tensor_core_kernel_and_the_float32_kernel_agree(models, tmp_path, monkeypatch):
