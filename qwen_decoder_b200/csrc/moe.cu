@@ -148,6 +148,72 @@ moe_topk_kernel(float* __restrict__ logits, int n_tokens, int E, int top, int mo
   for (int k = 0; k < top; k++) wt[(size_t)t * top + k] = v[k] / sum;
 }
 
+// The same choice with one warp per token (up to 256 router outputs: eight per lane, in registers): the softmax's
+// maximum and sum and every round's best output are warp reductions.  A round picks the largest value; of equal
+// values the lower index.
+#define MT_PER_LANE 8
+__global__ void __launch_bounds__(128)
+moe_topk_warp_kernel(const float* __restrict__ logits, int n_tokens, int E, int top, int mode,
+                     const float* __restrict__ corr, int* __restrict__ idx, float* __restrict__ wt) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= n_tokens) return;
+  const float* my = logits + (size_t)t * E;
+  float z[MT_PER_LANE], c[MT_PER_LANE];         // the value a weight is made from, and the value the choice goes by
+  float zmax = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < MT_PER_LANE; j++) {
+    const int e = lane + 32 * j;
+    z[j] = e < E ? my[e] : -INFINITY;
+    zmax = fmaxf(zmax, z[j]);
+  }
+  zmax = warp_max(zmax);
+  if (mode == 1) {
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < MT_PER_LANE; j++) { z[j] = lane + 32 * j < E ? expf(z[j] - zmax) : 0.f; sum += z[j]; }
+    const float inv = 1.0f / warp_sum(sum);
+#pragma unroll
+    for (int j = 0; j < MT_PER_LANE; j++) {
+      const int e = lane + 32 * j;
+      z[j] *= inv;                              // the score
+      c[j] = e < E ? z[j] + (corr ? corr[e] : 0.f) : -INFINITY;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < MT_PER_LANE; j++) c[j] = z[j];
+  }
+  float chosen = 0.f, first = 0.f, sum = 0.f;   // lane k keeps what round k chose
+  for (int k = 0; k < top; k++) {
+    float bv = -INFINITY, bz = 0.f;
+    int be = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < MT_PER_LANE; j++)       // ascending index within a lane: '>' keeps the lower one
+      if (c[j] > bv) { bv = c[j]; be = lane + 32 * j; bz = z[j]; }
+    if (bv == -INFINITY) be = 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o), oz = __shfl_xor_sync(0xffffffffu, bz, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; bz = oz; }
+    }
+#pragma unroll
+    for (int j = 0; j < MT_PER_LANE; j++)
+      if (lane + 32 * j == be) c[j] = -INFINITY;
+    if (k == 0) first = bz;
+    const float w = mode == 1 ? bz : expf(bz - first);          // mode 0: the first chosen is the largest logit
+    sum += w;
+    if (lane == (k & 31)) {
+      idx[(size_t)t * top + k] = be;
+      if (mode == 1) wt[(size_t)t * top + k] = w;
+      else chosen = w;                          // top <= 32: one round per lane
+    }
+  }
+  if (mode != 1 && lane < top) wt[(size_t)t * top + lane] = chosen / sum;
+}
+
 // ----------------------------------------------------------------------------- sort
 // One CTA.  meta: [0, E] offsets (E + 1), then n_tiles, then tiles (expert, first row, rows) x max_tiles.
 __global__ void __launch_bounds__(1024)
@@ -442,23 +508,46 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, c
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
+  __shared__ int s_row[MOE_MAX_TOP];            // the pair's row of y, or -1 for an identity expert
+  __shared__ float s_wt[MOE_MAX_TOP];
+  if (threadIdx.x < top) {
+    const size_t p = (size_t)t * top + threadIdx.x;
+    s_row[threadIdx.x] = (idx && idx[p] >= E_real) ? -1 : place[p];
+    s_wt[threadIdx.x] = wt[p];
+  }
+  __syncthreads();
+  const float sg = (shared && sgate) ? sgate[t] : 1.0f;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float acc = 0.f;
+#pragma unroll 4
     for (int k = 0; k < top; k++) {
-      const size_t p = (size_t)t * top + k;
-      const float v = (idx && idx[p] >= E_real) ? to_float(h[(size_t)t * D + i]) : y[(size_t)place[p] * D + i];
-      acc = fmaf(wt[p], v, acc);
+      const int row = s_row[k];
+      const float v = row < 0 ? to_float(h[(size_t)t * D + i]) : y[(size_t)row * D + i];
+      acc = fmaf(s_wt[k], v, acc);
     }
     if (shared) {
       float s = to_float(shared[(size_t)t * D + i]);
       for (int p = 1; p < n_parts; p++) s += to_float(shared[p * part_stride + (size_t)t * D + i]);
-      acc = sgate ? fmaf(sgate[t], s, acc) : acc + s;
+      acc = fmaf(sg, s, acc);
     }
     out[(size_t)t * D + i] = acc;
   }
 }
 
 // ----------------------------------------------------------------------------- launchers
+// The choice alone, from float32 logits [T, E] that a product left (the thread-per-token form overwrites them).
+extern "C" int qd_moe_topk(float* logits, int T, int E, int top, int mode, const float* corr, int* idx, float* wt,
+                           cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (top < 1 || top > E || top > MOE_MAX_TOP) return QD_ERR_UNSUPPORTED;
+  if (E <= 32 * MT_PER_LANE)
+    qd_launch(moe_topk_warp_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, (const float*)logits, T, E, top, mode, corr,
+              idx, wt);
+  else
+    qd_launch(moe_topk_kernel, dim3((T + 127) / 128), dim3(128), 0, stream, logits, T, E, top, mode, corr, idx, wt);
+  return qd_last_error();
+}
+
 // logits: float32 scratch [T, E] (left with the chosen entries at -inf)
 extern "C" int qd_moe_route(const void* h, const void* wr, const float* br, const void* wsg, int dtype, int T, int D,
                             int E, int top, int mode, const float* corr, float* logits, int* idx, float* wt,
@@ -476,8 +565,7 @@ extern "C" int qd_moe_route(const void* h, const void* wr, const float* br, cons
   else if (dtype == QD_BF16) { if (al && D % 8 == 0) MR_GO(bf16, true); else MR_GO(bf16, false); }
   else return QD_ERR_UNSUPPORTED;
 #undef MR_GO
-  qd_launch(moe_topk_kernel, dim3((T + 127) / 128), dim3(128), 0, stream, logits, T, E, top, mode, corr, idx, wt);
-  return qd_last_error();
+  return qd_moe_topk(logits, T, E, top, mode, corr, idx, wt, stream);
 }
 
 extern "C" int qd_moe_sort(const int* idx, int n_pairs, int E, int E_real, int tile_rows, int max_tiles, int* place,

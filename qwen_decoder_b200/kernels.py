@@ -859,6 +859,18 @@ def moe_route(h: torch.Tensor, wr: torch.Tensor, br: Optional[torch.Tensor], wsg
     _launch_count[0] += 1
 
 
+def moe_choose(logits: torch.Tensor, top: int, idx: torch.Tensor, wt: torch.Tensor, mode: int = MOE_ROUTE_TOP_SOFTMAX,
+               correction: Optional[torch.Tensor] = None) -> None:
+    """The choice of ``moe_route`` from float32 logits [T, E] that a product left (they may be overwritten)."""
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and idx.dtype == torch.int32 and wt.dtype == torch.float32
+    assert idx.shape == wt.shape == (T, top)
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == E)
+    _contig(logits, "logits")
+    _check(library("moe").qd_moe_topk(_ptr(logits), _I(T), _I(E), _I(top), _I(mode), _ptr(correction), _ptr(idx),
+                                      _ptr(wt), _stream()), "moe_choose")
+
+
 def moe_sort(idx: torch.Tensor, E: int, tile_rows: int, max_tiles: int, place: torch.Tensor, pair_at: torch.Tensor,
              meta: torch.Tensor, with_weights: Optional[int] = None) -> None:
     """Order the (token, choice) pairs by expert on the device: place[pair], pair_at[place], and ``meta`` =

@@ -24,6 +24,7 @@ from .. import kernels
 from ..config.registry import register_part
 from ..weights.loader import TensorSource, TensorSpec
 from .base import FeedForward
+from . import matmul_backend
 from .mlp import ACTIVATIONS, SwiGLU
 
 ROUTINGS = {"top_softmax": kernels.MOE_ROUTE_TOP_SOFTMAX, "softmax_all": kernels.MOE_ROUTE_SOFTMAX_ALL}
@@ -97,8 +98,15 @@ class RoutedExperts(FeedForward):
         idx = torch.empty((T, top), dtype=torch.int32, device=dev)
         wt = torch.empty((T, top), dtype=torch.float32, device=dev)
         sgate = torch.empty((T,), dtype=torch.float32, device=dev) if self.w_sg is not None else None
-        kernels.moe_route(x, self.w_router, self.b_router, self.w_sg, top, idx, wt, sgate, ROUTINGS[self.routing],
-                          self.correction)
+        if self.w_sg is None and self.b_router is None:
+            # no bias, no gate vector: the logits are a plain product (float32 sums of the engine's operands), by
+            # whichever kernel takes a product of this many tokens; then the choice
+            logits = torch.empty((T, O), dtype=torch.float32, device=dev)
+            matmul_backend.linear(x, self.w_router, None, logits)
+            kernels.moe_choose(logits, top, idx, wt, ROUTINGS[self.routing], self.correction)
+        else:
+            kernels.moe_route(x, self.w_router, self.b_router, self.w_sg, top, idx, wt, sgate, ROUTINGS[self.routing],
+                              self.correction)
         tile_rows = kernels.moe_tile_rows(n, E, D, F, x.dtype)   # rows of one expert a CTA takes
         max_tiles = n // tile_rows + E              # sum over experts of ceil(count / tile_rows) is at most this
         place = torch.empty((n,), dtype=torch.int32, device=dev)

@@ -116,8 +116,11 @@ class SinkAttention(Mixer):
             nd = T if ctx.all_decode else getattr(ctx, "num_decode", 0)
             if nd:
                 keys = ctx.max_context if ctx.all_decode else ctx.decode_max_context
+                # a CTA of this kernel keeps two key tiles in flight and one warp busy per token: two CTAs on
+                # every multiprocessor, about two tiles each
+                splits = decode_splits(nd * G, min(keys, window or keys), target_ctas=2 * kernels.sm_count())
                 kernels.sink_attention_mma(q, attn, cache.kv, cache.group.block_table, ctx.cu_tokens, ctx.start_pos,
-                                           nd, nd, *args, splits=decode_splits(nd * G, min(keys, window or keys)))
+                                           nd, nd, *args, splits=splits)
             if nd < T:
                 kernels.sink_attention_mma(q, attn, cache.kv, cache.group.block_table[nd:], ctx.cu_tokens[nd:],
                                            ctx.start_pos[nd:], ctx.num_requests - nd, T - nd, *args)
