@@ -278,9 +278,11 @@ VETERAX_SIZES = {
 }
 
 
-def veterax_configs(size):
+def veterax_configs(size, layers=None):
     from qwen_decoder_b200.config import config_from_dict
-    z = VETERAX_SIZES[size]
+    z = dict(VETERAX_SIZES[size])
+    if layers:                  # fewer layers of the same sizes (a capture under a profiler holds fewer weights)
+        z["layers"] = layers
     H, G = z["heads"]
     m = z["moe"]
     mixer = {"heads": H, "kv_heads": G, "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5, "v_mix": True,
@@ -442,7 +444,7 @@ def micro(args):
     if args.micro == "hybrid":
         return hybrid_bench(args)
     if args.micro == "veterax":
-        return hybrid_bench(args, "veterax", veterax_configs)
+        return hybrid_bench(args, "veterax", lambda size: veterax_configs(size, args.veterax_layers))
     if args.micro == "latent_attend":
         return latent_attend_micro(args)
     """One kernel alone: W-streaming contraction, decode attention or prefill attention at the 3B sizes."""
@@ -708,6 +710,7 @@ def main():
     ap.add_argument("--micro-splits", type=int, default=1, help="gemm with --micro-graph: shares of K (partial sums)")
     ap.add_argument("--hybrid-size", default="S", choices=["S", "M"], help="hybrid, veterax: which layer sizes")
     ap.add_argument("--only", default=None, choices=["hybrid", "dense"], help="hybrid, veterax: one of the two models (hybrid = the first)")
+    ap.add_argument("--veterax-layers", type=int, default=None, help="veterax: fewer layers than the size has")
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill"], help="hybrid: decode steps, the prompt, or both")
     ap.add_argument("--history", type=int, default=2048, help="mixed_step: cached tokens before the prompt portion")
     ap.add_argument("--stamps", action="store_true",

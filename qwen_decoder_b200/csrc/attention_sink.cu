@@ -244,8 +244,9 @@ extern "C" int qd_sink_attention_generic(const void* q, long long q_stride, void
 // weight enters P V as TWO bfloat16 numbers (p = hi + lo, two products into one float32 sum), so weights keep 16 bits
 // of mantissa.  Head sizes are padded with zero columns in shared memory up to the template's D (keys: 64, 128) and DV
 // (values: 64, 96, 128): any multiple of 8 up to 128 runs.  With ``splits`` > 1 the key tiles of a CTA's range are shared among
-// gridDim.z CTAs that leave (o, m, l) per row in scratch memory for ``sink_combine_kernel``, which also adds the
-// sink; with one split the kernel finishes the rows itself.
+// gridDim.z CTAs that leave (o, m, l) per row in scratch memory; the CTA that finishes last for a tile (a ticket per
+// tile) adds them up with the sink (``sink_combine_kernel`` does, where there are no tickets); with one split the kernel
+// finishes the rows itself.
 #define TS_ROWS 64
 #define TS_KEYS 64
 #define TS_PAD 8
@@ -303,7 +304,8 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
                           const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_tokens,
                           const int* __restrict__ start_pos, int n_requests, int H, int G, int d, int vd, int page_size,
                           float scale_log2, int window, const float* __restrict__ sinks, int splits,
-                          float* __restrict__ part_o, float* __restrict__ part_ml, int page_shift) {
+                          float* __restrict__ part_o, float* __restrict__ part_ml, int page_shift,
+                          unsigned* __restrict__ tickets) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int KP = D + TS_PAD, VP = DV + TS_PAD;          // row pitches in shared memory (bfloat16)
@@ -500,6 +502,57 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
             ts_pack(o[n][2 * half] * f, o[n][2 * half + 1] * f);
     }
   }
+  if (splits == 1 || tickets == nullptr) return;            // without tickets a combine kernel follows
+  // The CTA that finishes last for this tile adds up all splits.  Every thread has written its partial results; they
+  // meet, then one thread takes the ticket (its fence before the increment releases the CTA's writes, the fence
+  // after it acquires the others'), and the reads below go to L2, never to a stale line of this SM's L1.
+  __shared__ unsigned s_last;
+  __syncthreads();
+  if (tid == 0) {
+    unsigned* tk = tickets + (size_t)blockIdx.x * G + g;
+    __threadfence();
+    const unsigned got = atomicAdd(tk, 1u);
+    s_last = got == (unsigned)splits - 1;
+    if (s_last) *tk = 0;                                    // as found, for the next launch
+    __threadfence();
+  }
+  __syncthreads();
+  if (!s_last) return;
+  float* wgt = reinterpret_cast<float*>(Ks);                // [rows][splits] weights of the splits, then [rows] 1 / sum
+  const int rows_live = toks * gs;
+  float* inv_l = wgt + rows_live * splits;
+  if (tid < rows_live) {
+    const int tk_ = tid / gs, h = g * gs + (tid - tk_ * gs);
+    const size_t base = ((size_t)(t0 + tk_) * H + h) * splits;
+    const float sk = sinks ? sinks[h] * 1.4426950408889634f : -INFINITY;
+    float M = sk;
+    for (int s2 = 0; s2 < splits; s2++) M = fmaxf(M, __ldcg(part_ml + (base + s2) * 2));
+    float L = sinks ? exp2f(sk - M) : 0.f;
+    for (int s2 = 0; s2 < splits; s2++) {
+      const float m = __ldcg(part_ml + (base + s2) * 2);
+      const float w = m == -INFINITY ? 0.f : exp2f(m - M);
+      L += __ldcg(part_ml + (base + s2) * 2 + 1) * w;
+      wgt[tid * splits + s2] = w;
+    }
+    inv_l[tid] = 1.0f / L;
+  }
+  __syncthreads();
+  const int vd2 = vd >> 1;                                  // two elements per thread and turn
+  for (int idx = tid; idx < rows_live * vd2; idx += 128) {
+    const int row = idx / vd2, i = (idx - row * vd2) * 2;
+    const int tk_ = row / gs, h = g * gs + (row - tk_ * gs);
+    const size_t base = ((size_t)(t0 + tk_) * H + h) * splits;
+    float ax = 0.f, ay = 0.f;
+#pragma unroll 4
+    for (int s2 = 0; s2 < splits; s2++) {
+      const float2 v = __ldcg(reinterpret_cast<const float2*>(part_o + (base + s2) * vd + i));
+      const float w = wgt[row * splits + s2];
+      ax = fmaf(v.x, w, ax);
+      ay = fmaf(v.y, w, ay);
+    }
+    const float f = inv_l[row];
+    *reinterpret_cast<unsigned*>(out + (size_t)(t0 + tk_) * H * vd + (size_t)h * vd + i) = ts_pack(ax * f, ay * f);
+  }
 }
 
 // One warp per (token, head): the splits' (o, m, l) and the sink become the output row.  Lane s holds split s's
@@ -537,12 +590,13 @@ sink_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ 
 // q [n_tokens, H * d] and out [n_tokens, H * vd] bfloat16, dense; cu_tokens [n_requests + 1] rows of q / out per
 // request, start_pos [n_requests] the position of each request's first row; block_table [n_requests, max_blocks].
 // tiles: sum over requests of ceil(tokens / (64 / (H / G))) (an upper bound will do).  part_o [n_tokens * H * splits,
-// vd] and part_ml [n_tokens * H * splits, 2] float32 when splits > 1.
+// vd] and part_ml [n_tokens * H * splits, 2] float32 when splits > 1.  tickets: tiles * G zeroed words (every launch
+// leaves them zero) with which the last CTA of a tile adds up the splits itself; null: a combine kernel follows.
 extern "C" int qd_sink_attention_mma(const void* q, void* out, const void* kv, const int* block_table, int max_blocks,
                                      const int* cu_tokens, const int* start_pos, int n_requests, int n_tokens, int tiles,
                                      int H, int G, int d, int vd, int page_size, float scale, int window,
                                      const float* sinks, int splits, float* part_o, float* part_ml,
-                                     cudaStream_t stream) {
+                                     unsigned* tickets, cudaStream_t stream) {
   if (n_tokens <= 0 || n_requests <= 0) return 0;
   if (G <= 0 || H % G || H / G > TS_ROWS || d <= 0 || vd <= 0 || d > 128 || vd > 128 || d % 8 || vd % 8 ||
       page_size <= 0 || splits < 1 || splits > 64 || G > 65535 || (splits > 1 && (!part_o || !part_ml)))
@@ -562,7 +616,7 @@ extern "C" int qd_sink_attention_mma(const void* q, void* out, const void* kv, c
     }                                                                                                               \
     qd_launch(sink_attention_mma_kernel<D_, DV_>, grid, dim3(128), smem, stream, (const bf16*)q, (bf16*)out,          \
               (const bf16*)kv, block_table, max_blocks, cu_tokens, start_pos, n_requests, H, G, d, vd, page_size,    \
-              scale_log2, window, sinks, splits, part_o, part_ml, page_shift);                                       \
+              scale_log2, window, sinks, splits, part_o, part_ml, page_shift, tickets);                              \
   } while (0)
   if (d <= 64 && vd <= 64) TS_GO(64, 64);
   else if (d <= 64) TS_GO(64, 128);
@@ -570,7 +624,7 @@ extern "C" int qd_sink_attention_mma(const void* q, void* out, const void* kv, c
   else if (vd <= 96) TS_GO(128, 96);
   else TS_GO(128, 128);
 #undef TS_GO
-  if (splits > 1) {
+  if (splits > 1 && !tickets) {
     const int rows = n_tokens * H;
     qd_launch(sink_combine_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, (const float*)part_o,
               (const float*)part_ml, sinks, (bf16*)out, rows, H, vd, splits);

@@ -1059,16 +1059,20 @@ def sink_attention_mma(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, blo
     _contig(q, "q"); _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
     ntok = SINK_MMA_ROWS // (H // G)
     tiles = n_tokens // ntok + n_requests            # at least sum over requests of ceil(tokens / ntok)
-    part_o = part_ml = None
+    part_o = part_ml = tickets = None
     if splits > 1:
         rows = out.shape[0] * H
         part_o = torch.empty((rows * splits, vd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((rows * splits, 2), dtype=torch.float32, device=q.device)
+        if tiles * G <= _TICKETS:
+            tickets = _tickets.get(q.device)
+            if tickets is None:     # zero once; every launch leaves them zero again
+                tickets = _tickets[q.device] = torch.zeros(_TICKETS, dtype=torch.int32, device=q.device)
     _check(library("attention_sink").qd_sink_attention_mma(
         _ptr(q), _ptr(out), _ptr(kv), _ptr(block_table), _I(block_table.shape[1]), _ptr(cu_tokens), _ptr(start_pos),
         _I(n_requests), _I(n_tokens), _I(tiles), _I(H), _I(G), _I(d), _I(vd), _I(page_size), _F(scale), _I(window),
-        _ptr(sinks), _I(splits), _ptr(part_o), _ptr(part_ml), _stream()), "sink_attention_mma")
-    if splits > 1:
+        _ptr(sinks), _I(splits), _ptr(part_o), _ptr(part_ml), _ptr(tickets), _stream()), "sink_attention_mma")
+    if splits > 1 and tickets is None:
         _launch_count[0] += 1
 
 
