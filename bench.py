@@ -286,7 +286,7 @@ def veterax_configs(size, layers=None):
     H, G = z["heads"]
     m = z["moe"]
     mixer = {"heads": H, "kv_heads": G, "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5, "v_mix": True,
-             "rot": {"base": 500000.0, "dims": z["dim"], "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+             "rot": {"base": 1000000.0, "dims": z["dim"], "scaling": {"factor": 4.0, "original": 8192, "fast": 16.0, "slow": 2.0}}}
     mlp = {"kind": "moe", "expert": {"ff": m["ff"], "limit": 7.0}, "router": {"experts": m["experts"], "identity": m["identity"],
            "top": m["top"]}, "shared": {"ff": m["shared"], "limit": 7.0}}
     veterax = config_from_dict({"architecture": "Veterax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},

@@ -317,7 +317,8 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
   const int gs = H / G, ntok = TS_ROWS / gs;                // tokens of a tile
   const int g = blockIdx.y, split = blockIdx.z;
   // which request and which of its tiles
-  int r = 0, b = blockIdx.x, len = 0;
+  // the grid's first CTAs take the last tiles: with causal keys those stream the most, and they should not be the tail
+  int r = 0, b = gridDim.x - 1 - blockIdx.x, len = 0;
   for (; r < n_requests; r++) {
     len = cu_tokens[r + 1] - cu_tokens[r];
     const int tiles = (len + ntok - 1) / ntok;
@@ -409,17 +410,19 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
     const bf16* vs_ = Vs + (size_t)stage * TS_KEYS * VP;
     float s[TS_KEYS / 8][4];
 #pragma unroll
-    for (int n = 0; n < TS_KEYS / 8; n++) {
-      s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
-      // one instruction fetches the key tile's operands of two steps of 16 dimensions
-      const bf16* kp = ks_ + (n * 8 + (lane & 7)) * KP + (lane >> 3) * 8;
+    for (int n = 0; n < TS_KEYS / 8; n++) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    // Two steps of 16 dimensions at a time: one ldmatrix per group of 8 keys fetches both steps' operands, and the
+    // eight groups' products follow one another, so that no product waits for the one issued just before it.
 #pragma unroll
-      for (int ks = 0; ks < D / 16; ks += 2) {
-        unsigned kb[4];
-        ts_ldmatrix_x4(kb, kp + ks * 16);
-        ts_mma(s[n], qa[ks], kb[0], kb[1]);
-        ts_mma(s[n], qa[ks + 1], kb[2], kb[3]);
-      }
+    for (int ks = 0; ks < D / 16; ks += 2) {
+      unsigned kb[TS_KEYS / 8][4];
+#pragma unroll
+      for (int n = 0; n < TS_KEYS / 8; n++)
+        ts_ldmatrix_x4(kb[n], ks_ + (n * 8 + (lane & 7)) * KP + (lane >> 3) * 8 + ks * 16);
+#pragma unroll
+      for (int n = 0; n < TS_KEYS / 8; n++) ts_mma(s[n], qa[ks], kb[n][0], kb[n][1]);
+#pragma unroll
+      for (int n = 0; n < TS_KEYS / 8; n++) ts_mma(s[n], qa[ks + 1], kb[n][2], kb[n][3]);
     }
     // mask, scale (scores in units of log 2), row maxima
     float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -456,13 +459,18 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
       ts_split(s[2 * j + 1][0], s[2 * j + 1][1], ah[2], al[2]);
       ts_split(s[2 * j + 1][2], s[2 * j + 1][3], ah[3], al[3]);
 #pragma unroll
-      for (int n2 = 0; n2 < DV / 16; n2++) {
-        unsigned vb[4];
-        ts_ldmatrix_x4_trans(vb, vs_ + (j * 16 + (lane & 15)) * VP + n2 * 16 + (lane >> 4) * 8);
-        ts_mma(o[2 * n2], ah, vb[0], vb[1]);
-        ts_mma(o[2 * n2], al, vb[0], vb[1]);
-        ts_mma(o[2 * n2 + 1], ah, vb[2], vb[3]);
-        ts_mma(o[2 * n2 + 1], al, vb[2], vb[3]);
+      for (int n2 = 0; n2 < DV / 16; n2 += 2) {               // four output groups in flight: a sum is touched again
+        unsigned va[4], vb[4];                                // only after three products of other sums
+        ts_ldmatrix_x4_trans(va, vs_ + (j * 16 + (lane & 15)) * VP + n2 * 16 + (lane >> 4) * 8);
+        ts_ldmatrix_x4_trans(vb, vs_ + (j * 16 + (lane & 15)) * VP + (n2 + 1) * 16 + (lane >> 4) * 8);
+        ts_mma(o[2 * n2], ah, va[0], va[1]);
+        ts_mma(o[2 * n2 + 1], ah, va[2], va[3]);
+        ts_mma(o[2 * n2 + 2], ah, vb[0], vb[1]);
+        ts_mma(o[2 * n2 + 3], ah, vb[2], vb[3]);
+        ts_mma(o[2 * n2], al, va[0], va[1]);
+        ts_mma(o[2 * n2 + 1], al, va[2], va[3]);
+        ts_mma(o[2 * n2 + 2], al, vb[0], vb[1]);
+        ts_mma(o[2 * n2 + 3], al, vb[2], vb[3]);
       }
     }
     __syncthreads();          // all warps are done with this stage before the next fetch overwrites it

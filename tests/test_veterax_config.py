@@ -60,7 +60,7 @@ def test_cache_layout_keys_and_values_of_their_own_size():
     cm.check()
 
 
-@pytest.mark.parametrize("scaling", [None, vc.yarn(4.0, 64, 16.0, 2.0), vc.yarn(8.0, 512, 32.0, 1.0)])
+@pytest.mark.parametrize("scaling", [None, vc.yarn(4.0, 64, 16.0, 2.0), vc.yarn(5.0, 256, 20.0, 1.5)])
 def test_position_tables_follow_the_stretched_frequencies(scaling):
     rot = {"base": 500.0, "dims": 24, "scaling": scaling}
     part = Rotary(head_dim=32, rotary_dim=24, base=500.0, pairing="adjacent", scaling=scaling)

@@ -42,7 +42,7 @@ VA = config(300, 96, 1e-6, 8, [
 # kernel serves them in bfloat16 too), heads of 128, every layer mixes
 VB = config(515, 128, 2e-5, 0, [
     (attn(10, 1, 12, 20, rot_dims=4, base=300.0, v_mix=True), moe(7, 3, 32, 2.0, shared=(48, 1.0))),
-    (attn(2, 1, 128, 20, scaling=yarn(8.0, 128, 32.0, 1.0), scale=0.1, v_mix=True), moe(2, 2, 64, 1.2, identity=2)),
+    (attn(2, 1, 128, 20, scaling=yarn(6.0, 128, 24.0, 1.5), scale=0.1, v_mix=True), moe(2, 2, 64, 1.2, identity=2)),
     (attn(5, 1, 72, 20, rot_dims=36, v_mix=True), None),
 ])
 CONFIGS = {"A": VA, "B": VB}
