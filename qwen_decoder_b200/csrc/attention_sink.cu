@@ -305,7 +305,7 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
                           const int* __restrict__ start_pos, int n_requests, int H, int G, int d, int vd, int page_size,
                           float scale_log2, int window, const float* __restrict__ sinks, int splits,
                           float* __restrict__ part_o, float* __restrict__ part_ml, int page_shift,
-                          unsigned* __restrict__ tickets) {
+                          unsigned* __restrict__ tickets, int single_tokens) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int KP = D + TS_PAD, VP = DV + TS_PAD;          // row pitches in shared memory (bfloat16)
@@ -319,11 +319,17 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
   // which request and which of its tiles
   // the grid's first CTAs take the last tiles: with causal keys those stream the most, and they should not be the tail
   int r = 0, b = gridDim.x - 1 - blockIdx.x, len = 0;
-  for (; r < n_requests; r++) {
-    len = cu_tokens[r + 1] - cu_tokens[r];
-    const int tiles = (len + ntok - 1) / ntok;
-    if (b < tiles) break;
-    b -= tiles;
+  if (single_tokens) {                                      // every request brings one token: tile b is request b
+    r = b;
+    b = 0;
+    len = 1;
+  } else {
+    for (; r < n_requests; r++) {
+      len = cu_tokens[r + 1] - cu_tokens[r];
+      const int tiles = (len + ntok - 1) / ntok;
+      if (b < tiles) break;
+      b -= tiles;
+    }
   }
   if (r >= n_requests) return;
   const int tok0 = b * ntok, toks = min(ntok, len - tok0);  // tokens tok0 .. tok0 + toks - 1 of the request's portion
@@ -526,20 +532,31 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
   }
   __syncthreads();
   if (!s_last) return;
-  float* wgt = reinterpret_cast<float*>(Ks);                // [rows][splits] weights of the splits, then [rows] 1 / sum
+  // [rows][splits] the splits' maxima, then their weights in place; [rows][splits] their sums; [rows] 1 / total.
+  // Every (row, split) pair is fetched by a thread of its own, in one round of loads; a thread per row then sums up
+  // from shared memory.
+  float* wgt = reinterpret_cast<float*>(Ks);
   const int rows_live = toks * gs;
-  float* inv_l = wgt + rows_live * splits;
+  float* sums = wgt + rows_live * splits;
+  float* inv_l = sums + rows_live * splits;
+  for (int idx = tid; idx < rows_live * splits; idx += 128) {
+    const int row = idx / splits, s2 = idx - row * splits;
+    const int tk_ = row / gs, h = g * gs + (row - tk_ * gs);
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + ((size_t)(t0 + tk_) * H + h) * splits + s2);
+    wgt[idx] = ml.x;
+    sums[idx] = ml.y;
+  }
+  __syncthreads();
   if (tid < rows_live) {
     const int tk_ = tid / gs, h = g * gs + (tid - tk_ * gs);
-    const size_t base = ((size_t)(t0 + tk_) * H + h) * splits;
     const float sk = sinks ? sinks[h] * 1.4426950408889634f : -INFINITY;
     float M = sk;
-    for (int s2 = 0; s2 < splits; s2++) M = fmaxf(M, __ldcg(part_ml + (base + s2) * 2));
+    for (int s2 = 0; s2 < splits; s2++) M = fmaxf(M, wgt[tid * splits + s2]);
     float L = sinks ? exp2f(sk - M) : 0.f;
     for (int s2 = 0; s2 < splits; s2++) {
-      const float m = __ldcg(part_ml + (base + s2) * 2);
+      const float m = wgt[tid * splits + s2];
       const float w = m == -INFINITY ? 0.f : exp2f(m - M);
-      L += __ldcg(part_ml + (base + s2) * 2 + 1) * w;
+      L += sums[tid * splits + s2] * w;
       wgt[tid * splits + s2] = w;
     }
     inv_l[tid] = 1.0f / L;
@@ -551,7 +568,7 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
     const int tk_ = row / gs, h = g * gs + (row - tk_ * gs);
     const size_t base = ((size_t)(t0 + tk_) * H + h) * splits;
     float ax = 0.f, ay = 0.f;
-#pragma unroll 4
+#pragma unroll 8
     for (int s2 = 0; s2 < splits; s2++) {
       const float2 v = __ldcg(reinterpret_cast<const float2*>(part_o + (base + s2) * vd + i));
       const float w = wgt[row * splits + s2];
@@ -613,6 +630,8 @@ extern "C" int qd_sink_attention_mma(const void* q, void* out, const void* kv, c
   int page_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (page_shift = 0; (1 << page_shift) < page_size; page_shift++) {}
+  const int single_tokens = n_tokens == n_requests;         // every request has at least one token
+  if (single_tokens) tiles = n_requests;
   dim3 grid(tiles, G, splits);
 #define TS_GO(D_, DV_)                                                                                              \
   do {                                                                                                              \
@@ -624,7 +643,7 @@ extern "C" int qd_sink_attention_mma(const void* q, void* out, const void* kv, c
     }                                                                                                               \
     qd_launch(sink_attention_mma_kernel<D_, DV_>, grid, dim3(128), smem, stream, (const bf16*)q, (bf16*)out,          \
               (const bf16*)kv, block_table, max_blocks, cu_tokens, start_pos, n_requests, H, G, d, vd, page_size,    \
-              scale_log2, window, sinks, splits, part_o, part_ml, page_shift, tickets);                              \
+              scale_log2, window, sinks, splits, part_o, part_ml, page_shift, tickets, single_tokens);               \
   } while (0)
   if (d <= 64 && vd <= 64) TS_GO(64, 64);
   else if (d <= 64) TS_GO(64, 128);

@@ -28,7 +28,6 @@ from .. import kernels
 from ..cache import PagedKV
 from ..config.registry import register_part
 from ..weights.loader import TensorSource, TensorSpec
-from .attention import decode_splits
 from .base import Mixer, PagedCacheView
 from .linear import Linear
 
@@ -118,7 +117,7 @@ class SinkAttention(Mixer):
                 keys = ctx.max_context if ctx.all_decode else ctx.decode_max_context
                 # a CTA of this kernel keeps two key tiles in flight and one warp busy per token: two CTAs on
                 # every multiprocessor, about two tiles each
-                splits = decode_splits(nd * G, min(keys, window or keys), target_ctas=2 * kernels.sm_count())
+                splits = sink_decode_splits(nd * G, min(keys, window or keys))
                 kernels.sink_attention_mma(q, attn, cache.kv, cache.group.block_table, ctx.cu_tokens, ctx.start_pos,
                                            nd, nd, *args, splits=splits)
             if nd < T:
@@ -128,3 +127,12 @@ class SinkAttention(Mixer):
         kernels.sink_attention_generic(q, attn, cache.kv, cache.group.block_table, ctx.token_request, ctx.positions,
                                        H, G, d, vd, ps, self.scale, window, self.sinks)
         return self.out.forward_partial(attn)
+
+
+def sink_decode_splits(ctas_without_split: int, max_keys: int) -> int:
+    """CTAs per (token, KV head) of the tensor-core kernel for single tokens: as many as fill two CTAs on every
+    multiprocessor and never one more (a CTA that waits for a free place doubles the launch's time), none with fewer
+    than one tile of 64 keys, at most 64."""
+    by_fill = max(1, 2 * kernels.sm_count() // max(1, ctas_without_split))
+    by_work = max(1, (max_keys + 63) // 64)
+    return max(1, min(by_fill, by_work, 64))
