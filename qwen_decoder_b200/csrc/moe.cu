@@ -517,7 +517,8 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, c
   }
   __syncthreads();
   const float sg = (shared && sgate) ? sgate[t] : 1.0f;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+  // gridDim.y CTAs share a token's row: few tokens still fill the multiprocessors
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < D; i += gridDim.y * blockDim.x) {
     float acc = 0.f;
 #pragma unroll 4
     for (int k = 0; k < top; k++) {
@@ -642,8 +643,9 @@ extern "C" int qd_moe_combine(const float* y, const int* place, const float* wt,
                               cudaStream_t stream) {
   if (T <= 0) return 0;
   if (!h) idx = nullptr;
+  const int per_row = T >= 1024 ? 1 : (D + 255) / 256 < 16 ? (D + 255) / 256 : 16;
 #define MC_GO(TS, TH, NP, PS)                                                                                      \
-  qd_launch(moe_combine_kernel<TS, TH>, dim3(T), dim3(256), 0, stream, y, place, wt, top, (const TS*)shared, NP,    \
+  qd_launch(moe_combine_kernel<TS, TH>, dim3(T, per_row), dim3(256), 0, stream, y, place, wt, top, (const TS*)shared, NP, \
             (size_t)(PS), sgate, out, D, idx, E_real, (const TH*)h)
   const bool hb = h && h_dtype == QD_BF16;
   if (h && h_dtype != QD_BF16 && h_dtype != QD_F32) return QD_ERR_UNSUPPORTED;
