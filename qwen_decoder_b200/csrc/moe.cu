@@ -408,6 +408,12 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, const unsigned* a, cons
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+__device__ __forceinline__ void mm_ldmatrix_x4(unsigned* r, const void* smem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+
 #define MM_LD 40            // row pitch of a 32-element step in shared memory (bfloat16): no bank conflicts
 template <typename TO, bool GATED>
 __global__ void __launch_bounds__(128)
@@ -461,24 +467,20 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
     if (k0 + 32 < K) fetch(k0 + 32);
 #pragma unroll
     for (int ks = 0; ks < 32; ks += 16) {
+      // operands by ldmatrix: the warp's 16 rows of A in one instruction, two groups of 8 columns of W in one
       unsigned a[4];
-      const bf16* ap = As + (warp * 16 + g) * MM_LD + ks + 2 * tq;
-      a[0] = *reinterpret_cast<const unsigned*>(ap);
-      a[1] = *reinterpret_cast<const unsigned*>(ap + 8 * MM_LD);
-      a[2] = *reinterpret_cast<const unsigned*>(ap + 8);
-      a[3] = *reinterpret_cast<const unsigned*>(ap + 8 * MM_LD + 8);
+      mm_ldmatrix_x4(a, As + (warp * 16 + (lane & 15)) * MM_LD + ks + (lane >> 4) * 8);
 #pragma unroll
-      for (int j = 0; j < 8; j++) {
-        unsigned b[2];
-        const bf16* bp = B1 + (j * 8 + g) * MM_LD + ks + 2 * tq;
-        b[0] = *reinterpret_cast<const unsigned*>(bp);
-        b[1] = *reinterpret_cast<const unsigned*>(bp + 8);
+      for (int j = 0; j < 8; j += 2) {
+        unsigned b[4];
+        const int off = ((j + (lane >> 4)) * 8 + (lane & 7)) * MM_LD + ks + ((lane >> 3) & 1) * 8;
+        mm_ldmatrix_x4(b, B1 + off);
         mma_bf16_16816(c1[j], a, b);
+        mma_bf16_16816(c1[j + 1], a, b + 2);
         if (GATED) {
-          const bf16* bq = B2 + (j * 8 + g) * MM_LD + ks + 2 * tq;
-          b[0] = *reinterpret_cast<const unsigned*>(bq);
-          b[1] = *reinterpret_cast<const unsigned*>(bq + 8);
+          mm_ldmatrix_x4(b, B2 + off);
           mma_bf16_16816(c2[j], a, b);
+          mma_bf16_16816(c2[j + 1], a, b + 2);
         }
       }
     }
