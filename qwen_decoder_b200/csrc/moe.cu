@@ -400,7 +400,7 @@ moe_gemv_kernel(const TI* __restrict__ A, long long lda, const int* __restrict__
 
 // ----------------------------------------------------------------------------- many rows per expert, bfloat16
 // Tiles of 64 pairs x 64 output columns on the tensor cores (mma.sync m16n8k16, bfloat16 in, float32 sums), K in
-// steps of 32 through shared memory, the next step's 16-byte pieces fetched into registers while this one
+// steps of 64 through shared memory, the next step's 16-byte pieces fetched into registers while this one
 // multiplies.  Four warps, each 16 rows x 64 columns.  K must be a multiple of 8.
 __device__ __forceinline__ void mma_bf16_16816(float* c, const unsigned* a, const unsigned* b) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -414,7 +414,9 @@ __device__ __forceinline__ void mm_ldmatrix_x4(unsigned* r, const void* smem) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
 
-#define MM_LD 40            // row pitch of a 32-element step in shared memory (bfloat16): no bank conflicts
+#define MM_KS 64            // elements of K per step through shared memory
+#define MM_LD (MM_KS + 8)    // row pitch of a step in shared memory (bfloat16): no bank conflicts
+#define MM_PER (MM_KS / 16)  // 16-byte pieces of each tile a thread moves per step: 64 rows x MM_KS / 8 pieces over 128 threads
 template <typename TO, bool GATED>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ pair_at, int top, int by_token,
@@ -435,12 +437,13 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
   __syncthreads();
   const bf16* w1 = W1 + (size_t)e * N * K;
   const bf16* w2 = GATED ? W2 + (size_t)e * N * K : nullptr;
-  // each thread moves two 16-byte pieces of each tile per step: piece p = tid + 128 * i -> row p / 4, k (p % 4) * 8
-  uint4 ra[2], rb1[2], rb2[2];
+  // each thread moves MM_PER 16-byte pieces of each tile per step: piece p = tid + 128 * i -> row p / (MM_KS / 8),
+  // k (p % (MM_KS / 8)) * 8
+  uint4 ra[MM_PER], rb1[MM_PER], rb2[MM_PER];
   auto fetch = [&](int k0) {
 #pragma unroll
-    for (int i = 0; i < 2; i++) {
-      int p = tid + 128 * i, row = p >> 2, k = k0 + (p & 3) * 8;
+    for (int i = 0; i < MM_PER; i++) {
+      int p = tid + 128 * i, row = p / (MM_KS / 8), k = k0 + (p % (MM_KS / 8)) * 8;
       const uint4 zero = make_uint4(0, 0, 0, 0);
       ra[i] = (src[row] >= 0 && k < K) ? *reinterpret_cast<const uint4*>(A + (size_t)src[row] * lda + k) : zero;
       bool ok = n0 + row < N && k < K;
@@ -454,19 +457,19 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
 #pragma unroll
     for (int q = 0; q < 4; q++) { c1[j][q] = 0.f; if (GATED) c2[j][q] = 0.f; }
   fetch(0);
-  for (int k0 = 0; k0 < K; k0 += 32) {
+  for (int k0 = 0; k0 < K; k0 += MM_KS) {
     __syncthreads();                               // the step before has been read
 #pragma unroll
-    for (int i = 0; i < 2; i++) {
-      int p = tid + 128 * i, row = p >> 2, kc = (p & 3) * 8;
+    for (int i = 0; i < MM_PER; i++) {
+      int p = tid + 128 * i, row = p / (MM_KS / 8), kc = (p % (MM_KS / 8)) * 8;
       *reinterpret_cast<uint4*>(As + row * MM_LD + kc) = ra[i];
       *reinterpret_cast<uint4*>(B1 + row * MM_LD + kc) = rb1[i];
       if (GATED) *reinterpret_cast<uint4*>(B2 + row * MM_LD + kc) = rb2[i];
     }
     __syncthreads();
-    if (k0 + 32 < K) fetch(k0 + 32);
+    if (k0 + MM_KS < K) fetch(k0 + MM_KS);
 #pragma unroll
-    for (int ks = 0; ks < 32; ks += 16) {
+    for (int ks = 0; ks < MM_KS; ks += 16) {
       // operands by ldmatrix: the warp's 16 rows of A in one instruction, two groups of 8 columns of W in one
       unsigned a[4];
       mm_ldmatrix_x4(a, As + (warp * 16 + (lane & 15)) * MM_LD + ks + (lane >> 4) * 8);
