@@ -400,8 +400,8 @@ moe_gemv_kernel(const TI* __restrict__ A, long long lda, const int* __restrict__
 
 // ----------------------------------------------------------------------------- many rows per expert, bfloat16
 // Tiles of 64 pairs x 64 output columns on the tensor cores (mma.sync m16n8k16, bfloat16 in, float32 sums), K in
-// steps of 64 through shared memory, the next step's 16-byte pieces fetched into registers while this one
-// multiplies.  Four warps, each 16 rows x 64 columns.  K must be a multiple of 8.
+// steps of 64 through two stages of shared memory, the next step's 16-byte pieces on their way (cp.async) while this
+// one multiplies.  Four warps, each 16 rows x 64 columns.  K must be a multiple of 8.
 __device__ __forceinline__ void mma_bf16_16816(float* c, const unsigned* a, const unsigned* b) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -412,6 +412,11 @@ __device__ __forceinline__ void mm_ldmatrix_x4(unsigned* r, const void* smem) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+
+__device__ __forceinline__ void mm_cp_async16(void* smem, const void* gmem, int src_bytes) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(src_bytes));
 }
 
 #define MM_KS 64            // elements of K per step through shared memory
@@ -427,9 +432,12 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
   if ((int)blockIdx.y >= meta[E + 1]) return;
   const int* tile = meta + E + 2 + 3 * blockIdx.y;
   const int e = tile[0], row0 = tile[1], rows = tile[2];
-  __shared__ __align__(16) bf16 As[64 * MM_LD];
-  __shared__ __align__(16) bf16 B1[64 * MM_LD];
-  __shared__ __align__(16) bf16 B2[GATED ? 64 * MM_LD : 8];
+  // two stages of (A rows, W1 columns[, W2 columns]), each [64][MM_LD], filled by 16-byte cp.async
+  extern __shared__ __align__(16) unsigned char mm_raw[];
+  constexpr int TILE = 64 * MM_LD;
+  bf16* As_ = reinterpret_cast<bf16*>(mm_raw);
+  bf16* B1_ = As_ + 2 * TILE;
+  bf16* B2_ = B1_ + 2 * TILE;
   __shared__ int src[64];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
   const int n0 = blockIdx.x * 64;
@@ -438,17 +446,15 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
   const bf16* w1 = W1 + (size_t)e * N * K;
   const bf16* w2 = GATED ? W2 + (size_t)e * N * K : nullptr;
   // each thread moves MM_PER 16-byte pieces of each tile per step: piece p = tid + 128 * i -> row p / (MM_KS / 8),
-  // k (p % (MM_KS / 8)) * 8
-  uint4 ra[MM_PER], rb1[MM_PER], rb2[MM_PER];
-  auto fetch = [&](int k0) {
+  // k (p % (MM_KS / 8)) * 8; a piece outside the tile's rows, the matrix's columns or K is filled with zeros
+  auto fetch = [&](int k0, int st) {
 #pragma unroll
     for (int i = 0; i < MM_PER; i++) {
-      int p = tid + 128 * i, row = p / (MM_KS / 8), k = k0 + (p % (MM_KS / 8)) * 8;
-      const uint4 zero = make_uint4(0, 0, 0, 0);
-      ra[i] = (src[row] >= 0 && k < K) ? *reinterpret_cast<const uint4*>(A + (size_t)src[row] * lda + k) : zero;
-      bool ok = n0 + row < N && k < K;
-      rb1[i] = ok ? *reinterpret_cast<const uint4*>(w1 + (size_t)(n0 + row) * K + k) : zero;
-      if (GATED) rb2[i] = ok ? *reinterpret_cast<const uint4*>(w2 + (size_t)(n0 + row) * K + k) : zero;
+      const int p = tid + 128 * i, row = p / (MM_KS / 8), kc = (p % (MM_KS / 8)) * 8, k = k0 + kc;
+      const bool oka = src[row] >= 0 && k < K, okb = n0 + row < N && k < K;
+      mm_cp_async16(As_ + st * TILE + row * MM_LD + kc, oka ? A + (size_t)src[row] * lda + k : A, oka ? 16 : 0);
+      mm_cp_async16(B1_ + st * TILE + row * MM_LD + kc, okb ? w1 + (size_t)(n0 + row) * K + k : w1, okb ? 16 : 0);
+      if (GATED) mm_cp_async16(B2_ + st * TILE + row * MM_LD + kc, okb ? w2 + (size_t)(n0 + row) * K + k : w2, okb ? 16 : 0);
     }
   };
   float c1[8][4], c2[GATED ? 8 : 1][4];
@@ -456,18 +462,16 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
   for (int j = 0; j < 8; j++)
 #pragma unroll
     for (int q = 0; q < 4; q++) { c1[j][q] = 0.f; if (GATED) c2[j][q] = 0.f; }
-  fetch(0);
-  for (int k0 = 0; k0 < K; k0 += MM_KS) {
-    __syncthreads();                               // the step before has been read
-#pragma unroll
-    for (int i = 0; i < MM_PER; i++) {
-      int p = tid + 128 * i, row = p / (MM_KS / 8), kc = (p % (MM_KS / 8)) * 8;
-      *reinterpret_cast<uint4*>(As + row * MM_LD + kc) = ra[i];
-      *reinterpret_cast<uint4*>(B1 + row * MM_LD + kc) = rb1[i];
-      if (GATED) *reinterpret_cast<uint4*>(B2 + row * MM_LD + kc) = rb2[i];
-    }
+  fetch(0, 0);
+  asm volatile("cp.async.commit_group;\n" ::);
+  for (int k0 = 0, st = 0; k0 < K; k0 += MM_KS, st ^= 1) {
+    if (k0 + MM_KS < K) fetch(k0 + MM_KS, st ^ 1);
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group 1;\n" ::);  // this step's pieces have arrived (the next step's may be in flight)
     __syncthreads();
-    if (k0 + MM_KS < K) fetch(k0 + MM_KS);
+    const bf16* As = As_ + st * TILE;
+    const bf16* B1 = B1_ + st * TILE;
+    const bf16* B2 = B2_ + st * TILE;
 #pragma unroll
     for (int ks = 0; ks < MM_KS; ks += 16) {
       // operands by ldmatrix: the warp's 16 rows of A in one instruction, two groups of 8 columns of W in one
@@ -487,6 +491,7 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
         }
       }
     }
+    __syncthreads();                               // this stage has been read: the step after next may overwrite it
   }
 #pragma unroll
   for (int j = 0; j < 8; j++)
@@ -617,8 +622,16 @@ extern "C" int qd_moe_gemm(const void* A, long long lda, int a_dtype, const int*
   if (tile_rows == 64 && a_dtype == QD_BF16 && w_dtype == QD_BF16 && al16 && K % 8 == 0 && lda % 8 == 0) {
     // many rows per expert in bfloat16: tensor cores
 #define MM_GO(TO, G)                                                                                              \
-  qd_launch(moe_gemm_mma_kernel<TO, G>, grid, dim3(128), 0, stream, (const bf16*)A, lda, pair_at, top, by_token,  \
-            (const bf16*)W1, (const bf16*)W2, (TO*)out, N, K, meta, E, act)
+  do {                                                                                                            \
+    const size_t smem = (size_t)(G ? 3 : 2) * 2 * 64 * MM_LD * sizeof(bf16);                                      \
+    static bool raised = false;                                                                                   \
+    if (!raised && smem > 48 * 1024) {                                                                            \
+      cudaFuncSetAttribute(moe_gemm_mma_kernel<TO, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+      raised = true;                                                                                              \
+    }                                                                                                             \
+    qd_launch(moe_gemm_mma_kernel<TO, G>, grid, dim3(128), smem, stream, (const bf16*)A, lda, pair_at, top, by_token, \
+              (const bf16*)W1, (const bf16*)W2, (TO*)out, N, K, meta, E, act);                                    \
+  } while (0)
     if (out_dtype == QD_BF16) { if (gated) MM_GO(bf16, true); else MM_GO(bf16, false); }
     else if (out_dtype == QD_F32) { if (gated) MM_GO(float, true); else MM_GO(float, false); }
     else return QD_ERR_UNSUPPORTED;
